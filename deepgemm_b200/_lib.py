@@ -1,0 +1,100 @@
+"""ctypes binding of libmegamoe_b200.so (the C ABI declared in include/megamoe_b200.h).
+
+There is no fallback: if the shared object is missing or a call fails, an exception is raised.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import POINTER, c_char_p, c_float, c_int, c_int32, c_int64, c_uint64, c_void_p
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libmegamoe_b200.so")
+
+# enum mirrors of include/megamoe_b200.h
+SYM_NAMES = ["peer_ptrs", "signals", "runtime_num_tokens", "count_matrix", "x", "x_sf", "topk_idx", "topk_weights",
+             "pool_x", "pool_meta", "combine", "pool_rows"]
+SCR_NAMES = ["status", "epoch", "plan", "block_counts", "dest_base", "expert_total", "expert_off", "mblock_expert",
+             "mblock_valid", "dest_row", "row_amax", "act_scale", "act_bf16", "act_fp8", "route_blocks"]
+MODE_STAGED, MODE_FUSED = 0, 1
+MAX_RANKS = 16
+BLOCK_M = 128
+
+STATUS_NAMES = {0: "ok", 1: "rank barrier timeout", 2: "GEMM pipeline timeout", 3: "receive pool overflow",
+                4: "grid barrier timeout"}
+
+# every symbol the header declares, with its signature
+_SIGNATURES = {
+    "mm_last_error": (c_char_p, []),
+    "mm_token_alignment": (c_int, []),
+    "mm_symm_buffer_layout": (c_int, [c_int] * 6 + [POINTER(c_int64), POINTER(c_int64)]),
+    "mm_scratch_layout": (c_int, [c_int] * 6 + [POINTER(c_int64), POINTER(c_int64)]),
+    "mm_ipc_alloc": (c_int, [c_int64, POINTER(c_void_p), c_void_p]),
+    "mm_ipc_open": (c_int, [c_void_p, POINTER(c_void_p)]),
+    "mm_ipc_close": (c_int, [c_void_p]),
+    "mm_ipc_free": (c_int, [c_void_p]),
+    "mm_init_buffers": (c_int, [c_void_p, c_void_p, POINTER(c_uint64), c_int] + [c_int] * 6 + [c_void_p]),
+    "mm_quant_per_token": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p]),
+    "mm_fp8_w8a8_mega_moe": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                     POINTER(c_uint64), c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                                     c_int, c_void_p, c_void_p]),
+    "mm_read_status": (c_int, [c_void_p, c_void_p, POINTER(c_int32)]),
+    "mm_set_timeouts": (c_int, [c_int, c_int]),
+    "mm_build_config": (c_int, [ctypes.c_char_p, c_int]),
+    "mm_launch_count": (c_int64, []),
+}
+EXPORTED_SYMBOLS = tuple(_SIGNATURES)
+
+_lib = None
+
+
+class MegaMoeError(RuntimeError):
+    pass
+
+
+def lib() -> ctypes.CDLL:
+    """Load the shared object (once).  Raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise MegaMoeError(
+                f"{LIB_PATH} is missing: build it with `python -m deepgemm_b200.build` "
+                "(there is no CPU or PyTorch fallback for this operator)")
+        handle = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in _SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = handle
+    return _lib
+
+
+def check(rc: int) -> None:
+    if rc != 0:
+        msg = lib().mm_last_error()
+        raise MegaMoeError(f"libmegamoe_b200 error {rc}: {msg.decode() if msg else '?'}")
+
+
+def symm_buffer_layout(R, E, T, K, H, I):
+    offs = (c_int64 * len(SYM_NAMES))()
+    total = c_int64()
+    check(lib().mm_symm_buffer_layout(R, E, T, K, H, I, offs, ctypes.byref(total)))
+    return dict(zip(SYM_NAMES, offs)), total.value
+
+
+def scratch_layout(R, E, T, K, H, I):
+    offs = (c_int64 * len(SCR_NAMES))()
+    total = c_int64()
+    check(lib().mm_scratch_layout(R, E, T, K, H, I, offs, ctypes.byref(total)))
+    return dict(zip(SCR_NAMES, offs)), total.value
+
+
+def build_config() -> dict:
+    import json
+    buf = ctypes.create_string_buffer(1024)
+    check(lib().mm_build_config(buf, 1024))
+    return json.loads(buf.value.decode())
+
+
+def launch_count() -> int:
+    return int(lib().mm_launch_count())

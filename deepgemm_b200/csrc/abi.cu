@@ -1,0 +1,376 @@
+// extern "C" entry points of libmegamoe_b200.so (declared in include/megamoe_b200.h) and the host-side launch logic.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <atomic>
+#include <mutex>
+#include <vector>
+
+#include "../../include/megamoe_b200.h"
+#include "gemm.cuh"
+#include "layout.h"
+#include "misc.cuh"
+#include "route.cuh"
+
+static_assert(MM_ABI_MAX_RANKS == MM_MAX_RANKS, "header and layout disagree");
+
+namespace {
+
+thread_local char g_err[512] = "";
+std::atomic<int64_t> g_launches{0};
+std::atomic<int> g_barrier_ms{30000};
+std::atomic<int> g_pipe_ms{4000};
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+#define MM_CUDA(expr)                                                                          \
+    do {                                                                                       \
+        cudaError_t _e = (expr);                                                               \
+        if (_e != cudaSuccess) return fail(100 + (int)_e, "%s failed: %s", #expr, cudaGetErrorString(_e)); \
+    } while (0)
+
+#define MM_REQUIRE(cond, ...)                 \
+    do {                                      \
+        if (!(cond)) return fail(1, __VA_ARGS__); \
+    } while (0)
+
+int check_shape(int R, int E, int T, int K, int H, int I) {
+    MM_REQUIRE(R > 0 && R <= MM_MAX_RANKS, "num_ranks must be in 1..%d", MM_MAX_RANKS);
+    MM_REQUIRE(E > 0 && E % R == 0, "num_experts must be divisible by num_ranks");
+    MM_REQUIRE(E <= MM_MAX_EXPERTS, "num_experts must be <= %d", MM_MAX_EXPERTS);
+    MM_REQUIRE(T >= 0, "num_max_tokens_per_rank must be non-negative");
+    MM_REQUIRE(K > 0 && K <= MM_MAX_TOPK, "num_topk must be in 1..%d", MM_MAX_TOPK);
+    MM_REQUIRE(H > 0 && I > 0, "hidden sizes must be positive");
+    MM_REQUIRE(H % 128 == 0 && I % 128 == 0, "hidden and intermediate_hidden must be multiples of 128");
+    MM_REQUIRE((int64_t)R * T * K < (1ll << 30), "capacity too large");
+    return 0;
+}
+
+// ------------------------------------------------------------------------------------------ tensor maps
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+int get_encode_fn(EncodeTiledFn* out) {
+    static EncodeTiledFn fn = nullptr;
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lk(mu);
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        MM_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres));
+        MM_REQUIRE(p != nullptr && qres == cudaDriverEntryPointSuccess, "cuTensorMapEncodeTiled is not available in this driver");
+        fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    *out = fn;
+    return 0;
+}
+
+struct MapKey { const void* ptr; uint64_t inner, rows; };
+struct MapEntry { MapKey key; CUtensorMap map; };
+std::mutex g_map_mu;
+std::vector<MapEntry> g_maps;
+
+// 2-D row-major byte matrix [rows][inner], box = 128 rows x 128 bytes, 128-byte swizzle.
+int tensor_map_2d(const void* ptr, uint64_t inner, uint64_t rows, CUtensorMap* out) {
+    {
+        std::lock_guard<std::mutex> lk(g_map_mu);
+        for (auto& m : g_maps)
+            if (m.key.ptr == ptr && m.key.inner == inner && m.key.rows == rows) { *out = m.map; return 0; }
+    }
+    EncodeTiledFn enc;
+    if (int rc = get_encode_fn(&enc)) return rc;
+    MM_REQUIRE((reinterpret_cast<uintptr_t>(ptr) & 15) == 0, "tensor base must be 16-byte aligned");
+    MM_REQUIRE(inner % 16 == 0, "row pitch must be a multiple of 16 bytes");
+    cuuint64_t dims[2] = {inner, rows};
+    cuuint64_t strides[1] = {inner};
+    cuuint32_t box[2] = {128, 128};
+    cuuint32_t estr[2] = {1, 1};
+    CUtensorMap map;
+    CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    MM_REQUIRE(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    std::lock_guard<std::mutex> lk(g_map_mu);
+    if (g_maps.size() > 256) g_maps.clear();
+    g_maps.push_back({{ptr, inner, rows}, map});
+    *out = map;
+    return 0;
+}
+
+int sm_count(int* out) {
+    int dev = 0;
+    MM_CUDA(cudaGetDevice(&dev));
+    static int cached[64] = {0};
+    if (dev < 64 && cached[dev]) { *out = cached[dev]; return 0; }
+    int n = 0;
+    MM_CUDA(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
+    if (dev < 64) cached[dev] = n;
+    *out = n;
+    return 0;
+}
+
+int ensure_gemm_attrs() {
+    static std::mutex mu;
+    static bool done[64] = {false};
+    int dev = 0;
+    MM_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lk(mu);
+    if (dev < 64 && done[dev]) return 0;
+    MM_CUDA(cudaFuncSetAttribute(mm::grouped_gemm_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, mm::kGemmSmemBytes));
+    MM_CUDA(cudaFuncSetAttribute(mm::grouped_gemm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, mm::kGemmSmemBytes));
+    if (dev < 64) done[dev] = true;
+    return 0;
+}
+
+#define MM_LAUNCHED()                 \
+    do {                              \
+        g_launches.fetch_add(1);      \
+        MM_CUDA(cudaGetLastError());  \
+    } while (0)
+
+}  // namespace
+
+extern "C" {
+
+const char* mm_last_error(void) { return g_err; }
+
+int mm_token_alignment(void) { return MM_TOKEN_ALIGNMENT; }
+
+int mm_symm_buffer_layout(int R, int E, int T, int K, int H, int I, int64_t* offsets, int64_t* total_bytes) {
+    if (int rc = check_shape(R, E, T, K, H, I)) return rc;
+    const MmSymLayout L = mm_sym_layout(R, E, T, K, H, I);
+    if (offsets) {
+        offsets[MM_SYM_PEER_PTRS] = L.peer_ptrs; offsets[MM_SYM_SIGNALS] = L.signals;
+        offsets[MM_SYM_RUNTIME_NUM_TOKENS] = L.runtime_num_tokens; offsets[MM_SYM_COUNT_MATRIX] = L.count_matrix;
+        offsets[MM_SYM_X] = L.x; offsets[MM_SYM_X_SF] = L.x_sf; offsets[MM_SYM_TOPK_IDX] = L.topk_idx;
+        offsets[MM_SYM_TOPK_WEIGHTS] = L.topk_weights; offsets[MM_SYM_POOL_X] = L.pool_x; offsets[MM_SYM_POOL_META] = L.pool_meta;
+        offsets[MM_SYM_COMBINE] = L.combine; offsets[MM_SYM_POOL_ROWS] = L.pool_rows;
+    }
+    if (total_bytes) *total_bytes = L.total;
+    return 0;
+}
+
+int mm_scratch_layout(int R, int E, int T, int K, int H, int I, int64_t* offsets, int64_t* total_bytes) {
+    if (int rc = check_shape(R, E, T, K, H, I)) return rc;
+    const MmScratchLayout L = mm_scratch_layout_of(R, E, T, K, H, I);
+    if (offsets) {
+        offsets[MM_SCR_STATUS] = L.status; offsets[MM_SCR_EPOCH] = L.epoch; offsets[MM_SCR_PLAN] = L.plan;
+        offsets[MM_SCR_BLOCK_COUNTS] = L.block_counts; offsets[MM_SCR_DEST_BASE] = L.dest_base;
+        offsets[MM_SCR_EXPERT_TOTAL] = L.expert_total; offsets[MM_SCR_EXPERT_OFF] = L.expert_off;
+        offsets[MM_SCR_MBLOCK_EXPERT] = L.mblock_expert; offsets[MM_SCR_MBLOCK_VALID] = L.mblock_valid;
+        offsets[MM_SCR_DEST_ROW] = L.dest_row; offsets[MM_SCR_ROW_AMAX] = L.row_amax; offsets[MM_SCR_ACT_SCALE] = L.act_scale;
+        offsets[MM_SCR_ACT_BF16] = L.act_bf16; offsets[MM_SCR_ACT_FP8] = L.act_fp8; offsets[MM_SCR_ROUTE_BLOCKS] = L.route_blocks;
+    }
+    if (total_bytes) *total_bytes = L.total;
+    return 0;
+}
+
+int mm_ipc_alloc(int64_t bytes, void** dev_ptr, void* handle64) {
+    MM_REQUIRE(bytes > 0 && dev_ptr != nullptr, "mm_ipc_alloc: bad arguments");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle is 64 bytes");
+    void* p = nullptr;
+    MM_CUDA(cudaMalloc(&p, (size_t)bytes));
+    if (handle64) {
+        cudaIpcMemHandle_t h;
+        cudaError_t e = cudaIpcGetMemHandle(&h, p);
+        if (e != cudaSuccess) {
+            cudaFree(p);
+            return fail(100 + (int)e, "cudaIpcGetMemHandle failed: %s", cudaGetErrorString(e));
+        }
+        memcpy(handle64, &h, 64);
+    }
+    *dev_ptr = p;
+    return 0;
+}
+
+int mm_ipc_open(const void* handle64, void** dev_ptr) {
+    MM_REQUIRE(handle64 != nullptr && dev_ptr != nullptr, "mm_ipc_open: bad arguments");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, 64);
+    MM_CUDA(cudaIpcOpenMemHandle(dev_ptr, h, cudaIpcMemLazyEnablePeerAccess));
+    return 0;
+}
+
+int mm_ipc_close(void* dev_ptr) {
+    if (dev_ptr) MM_CUDA(cudaIpcCloseMemHandle(dev_ptr));
+    return 0;
+}
+
+int mm_ipc_free(void* dev_ptr) {
+    if (dev_ptr) MM_CUDA(cudaFree(dev_ptr));
+    return 0;
+}
+
+int mm_init_buffers(void* sym_base, void* scratch, const uint64_t* peer_ptrs, int rank, int R, int E, int T, int K, int H,
+                    int I, void* stream_) {
+    if (int rc = check_shape(R, E, T, K, H, I)) return rc;
+    MM_REQUIRE(sym_base && scratch && peer_ptrs, "mm_init_buffers: null pointer");
+    MM_REQUIRE(rank >= 0 && rank < R, "rank out of range");
+    MM_REQUIRE(peer_ptrs[rank] == reinterpret_cast<uint64_t>(sym_base), "peer_ptrs[rank] must be the local buffer");
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    const MmSymLayout sl = mm_sym_layout(R, E, T, K, H, I);
+    const MmScratchLayout cl = mm_scratch_layout_of(R, E, T, K, H, I);
+    uint8_t* s = static_cast<uint8_t*>(sym_base);
+    uint8_t* c = static_cast<uint8_t*>(scratch);
+    MM_CUDA(cudaMemsetAsync(s, 0, (size_t)sl.x, stream));                                 // header .. count matrix
+    MM_CUDA(cudaMemsetAsync(c, 0, (size_t)cl.dest_row, stream));                          // status .. m-block tables
+    MM_CUDA(cudaMemsetAsync(c + cl.row_amax, 0, (size_t)(cl.act_bf16 - cl.row_amax), stream));
+    uint64_t table[MM_MAX_RANKS] = {0};
+    for (int r = 0; r < R; ++r) table[r] = peer_ptrs[r];
+    MM_CUDA(cudaMemcpyAsync(s + sl.peer_ptrs, table, sizeof(table), cudaMemcpyHostToDevice, stream));
+    MM_CUDA(cudaStreamSynchronize(stream));   // `table` lives on this stack frame
+    return 0;
+}
+
+int mm_quant_per_token(const void* x_bf16, int64_t rows, int k, void* out_fp8, float* out_scale, void* stream_) {
+    MM_REQUIRE(rows >= 0 && k > 0 && k % 8 == 0, "mm_quant_per_token: k must be a positive multiple of 8");
+    if (rows == 0) return 0;
+    MM_REQUIRE(x_bf16 && out_fp8 && out_scale, "mm_quant_per_token: null pointer");
+    MM_REQUIRE((reinterpret_cast<uintptr_t>(x_bf16) & 15) == 0 && (reinterpret_cast<uintptr_t>(out_fp8) & 7) == 0,
+               "mm_quant_per_token: pointers must be 16-byte (input) and 8-byte (output) aligned");
+    int sms = 0;
+    if (int rc = sm_count(&sms)) return rc;
+    int64_t blocks = (rows + 7) / 8;
+    if (blocks > (int64_t)sms * 8) blocks = (int64_t)sms * 8;
+    mm::quant_per_token_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream_)>>>(
+        static_cast<const __nv_bfloat16*>(x_bf16), rows, k, static_cast<uint8_t*>(out_fp8), out_scale);
+    MM_LAUNCHED();
+    return 0;
+}
+
+int mm_fp8_w8a8_mega_moe(void* y, const void* w1, const float* s1, const void* w2, const float* s2, int* stats, void* sym_base,
+                         void* scratch, const uint64_t* peer_ptrs, int rank, int R, int T_max, int E_loc, int num_tokens,
+                         int K, int H, int I, float activation_clamp, int mode, const int* runtime_num_tokens, void* stream_) {
+    MM_REQUIRE(E_loc > 0, "num_experts_per_rank must be positive");
+    const int E = E_loc * R;
+    if (int rc = check_shape(R, E, T_max, K, H, I)) return rc;
+    MM_REQUIRE(y && w1 && s1 && w2 && s2 && sym_base && scratch && peer_ptrs, "mm_fp8_w8a8_mega_moe: null pointer");
+    MM_REQUIRE(rank >= 0 && rank < R, "rank out of range");
+    MM_REQUIRE(num_tokens >= 0 && num_tokens <= T_max, "too many tokens");
+    MM_REQUIRE(peer_ptrs[rank] == reinterpret_cast<uint64_t>(sym_base), "peer_ptrs[rank] must be the local buffer");
+    MM_REQUIRE(!isnan(activation_clamp) && activation_clamp > 0.0f, "activation_clamp must be positive (+inf for none)");
+    MM_REQUIRE(mode == MM_MODE_STAGED || mode == MM_MODE_FUSED, "unknown mode");
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+
+    mm::RouteParams rp;
+    memset(&rp, 0, sizeof(rp));
+    rp.sym = static_cast<uint8_t*>(sym_base);
+    rp.scratch = static_cast<uint8_t*>(scratch);
+    for (int r = 0; r < R; ++r) rp.peers[r] = peer_ptrs[r];
+    rp.sl = mm_sym_layout(R, E, T_max, K, H, I);
+    rp.cl = mm_scratch_layout_of(R, E, T_max, K, H, I);
+    rp.rank = rank; rp.R = R; rp.E = E; rp.E_loc = E_loc; rp.T = T_max; rp.K = K; rp.H = H;
+    rp.num_tokens = num_tokens;
+    rp.runtime_num_tokens = runtime_num_tokens;
+    rp.stats = stats;
+    rp.barrier_timeout_ns = (uint64_t)g_barrier_ms.load() * 1000000ull;
+    // with a device-side token count every block that could own a route must run
+    const int64_t tokens_bound = runtime_num_tokens ? T_max : num_tokens;
+    int route_blocks = (int)((tokens_bound * K + MM_ROUTE_CHUNK - 1) / MM_ROUTE_CHUNK);
+    if (route_blocks < 1) route_blocks = 1;
+    rp.cl.route_blocks = route_blocks;   // blocks whose histogram rows are live in this call
+
+    int sms = 0;
+    if (int rc = sm_count(&sms)) return rc;
+    if (int rc = ensure_gemm_attrs()) return rc;
+
+    uint8_t* sc = rp.scratch;
+    CUtensorMap tm_pool, tm_w1, tm_act, tm_w2;
+    if (int rc = tensor_map_2d(rp.sym + rp.sl.pool_x, (uint64_t)H, (uint64_t)rp.sl.pool_rows, &tm_pool)) return rc;
+    if (int rc = tensor_map_2d(w1, (uint64_t)H, (uint64_t)E_loc * 2 * I, &tm_w1)) return rc;
+    if (int rc = tensor_map_2d(sc + rp.cl.act_fp8, (uint64_t)I, (uint64_t)rp.sl.pool_rows, &tm_act)) return rc;
+    if (int rc = tensor_map_2d(w2, (uint64_t)I, (uint64_t)E_loc * H, &tm_w2)) return rc;
+
+    mm::GemmParams g1;
+    memset(&g1, 0, sizeof(g1));
+    g1.plan = reinterpret_cast<const int*>(sc + rp.cl.plan);
+    g1.mblock_expert = reinterpret_cast<const int*>(sc + rp.cl.mblock_expert);
+    g1.mblock_valid = reinterpret_cast<const int*>(sc + rp.cl.mblock_valid);
+    g1.meta = reinterpret_cast<const MmPoolMeta*>(rp.sym + rp.sl.pool_meta);
+    g1.status = reinterpret_cast<int*>(sc + rp.cl.status);
+    g1.timeout_ns = (uint64_t)g_pipe_ms.load() * 1000000ull;
+    for (int r = 0; r < R; ++r) g1.peers[r] = peer_ptrs[r];
+    g1.combine_off = rp.sl.combine;
+    g1.T = T_max; g1.H = H;
+    g1.act_bf16 = reinterpret_cast<__nv_bfloat16*>(sc + rp.cl.act_bf16);
+    g1.row_amax = reinterpret_cast<unsigned int*>(sc + rp.cl.row_amax);
+    g1.act_scale = reinterpret_cast<const float*>(sc + rp.cl.act_scale);
+    g1.clamp = activation_clamp;
+    mm::GemmParams g2 = g1;
+    g1.kdim = H; g1.n_blocks = I / 128; g1.n_out = I; g1.w_rows_per_expert = 2 * I; g1.w_scale = s1;
+    g2.kdim = I; g2.n_blocks = (H + mm::kBlockN - 1) / mm::kBlockN; g2.n_out = H; g2.w_rows_per_expert = H; g2.w_scale = s2;
+
+    if (mode == MM_MODE_FUSED) return fail(2, "the fused variant is not available in this build");
+
+    mm::route_count_kernel<<<route_blocks, MM_ROUTE_CHUNK, 0, stream>>>(rp);
+    MM_LAUNCHED();
+    mm::route_exchange_kernel<<<1, 1024, 0, stream>>>(rp);
+    MM_LAUNCHED();
+    mm::route_plan_kernel<<<1, 1024, 0, stream>>>(rp);
+    MM_LAUNCHED();
+    mm::dispatch_kernel<<<route_blocks, MM_ROUTE_CHUNK, 0, stream>>>(rp);
+    MM_LAUNCHED();
+    if (R > 1) {
+        mm::rank_barrier_kernel<<<1, 32, 0, stream>>>(rp, MM_BAR_DISPATCH);
+        MM_LAUNCHED();
+    }
+    mm::grouped_gemm_kernel<0><<<sms, mm::kGemmThreads, mm::kGemmSmemBytes, stream>>>(tm_pool, tm_w1, g1);
+    MM_LAUNCHED();
+    mm::requant_kernel<<<sms * 8, 256, 0, stream>>>(g1.act_bf16, I, g1.plan, g1.mblock_valid, g1.row_amax,
+                                                   reinterpret_cast<float*>(sc + rp.cl.act_scale), sc + rp.cl.act_fp8);
+    MM_LAUNCHED();
+    mm::grouped_gemm_kernel<1><<<sms, mm::kGemmThreads, mm::kGemmSmemBytes, stream>>>(tm_act, tm_w2, g2);
+    MM_LAUNCHED();
+    if (R > 1) {
+        mm::rank_barrier_kernel<<<1, 32, 0, stream>>>(rp, MM_BAR_COMBINE);
+        MM_LAUNCHED();
+    }
+    mm::combine_reduce_kernel<<<sms * 8, 256, 0, stream>>>(rp.sym, rp.sl, E, T_max, K, H, num_tokens, runtime_num_tokens,
+                                                          static_cast<__nv_bfloat16*>(y));
+    MM_LAUNCHED();
+    return 0;
+}
+
+int mm_read_status(const void* scratch, void* stream_, int32_t* out5) {
+    MM_REQUIRE(scratch && out5, "mm_read_status: null pointer");
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    MM_CUDA(cudaMemcpyAsync(out5, scratch, 5 * sizeof(int32_t), cudaMemcpyDeviceToHost, stream));
+    MM_CUDA(cudaStreamSynchronize(stream));
+    return 0;
+}
+
+int mm_set_timeouts(int rank_barrier_ms, int pipeline_ms) {
+    MM_REQUIRE(rank_barrier_ms > 0 && pipeline_ms > 0, "timeouts must be positive");
+    g_barrier_ms.store(rank_barrier_ms);
+    g_pipe_ms.store(pipeline_ms);
+    return 0;
+}
+
+int mm_build_config(char* json, int capacity) {
+    MM_REQUIRE(json && capacity > 0, "mm_build_config: bad arguments");
+    const int n = snprintf(json, (size_t)capacity,
+                           "{\"operator\": \"fp8_w8a8_mega_moe\", \"package\": \"megamoe\", \"arch\": \"sm_100a\", "
+                           "\"weight_scale_mode\": \"channelwise_fp32\", \"input_scale_mode\": \"channelwise_fp32\", "
+                           "\"l2_act_scale_mode\": \"channelwise_fp32\", \"has_fp8_api\": true, \"has_fp4_api\": false, "
+                           "\"fusion_boundary\": \"dispatch_pool_l1_swiglu_quant_l2_combine\", "
+                           "\"block_m\": %d, \"block_n\": %d, \"block_k\": %d, \"stages\": %d, \"token_alignment\": %d, "
+                           "\"max_ranks\": %d}",
+                           mm::kBlockM, mm::kBlockN, mm::kBlockK, mm::kStages, MM_TOKEN_ALIGNMENT, MM_MAX_RANKS);
+    MM_REQUIRE(n > 0 && n < capacity, "mm_build_config: buffer too small");
+    return 0;
+}
+
+int64_t mm_launch_count(void) { return g_launches.load(); }
+
+}  // extern "C"

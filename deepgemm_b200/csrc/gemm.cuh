@@ -1,0 +1,313 @@
+// Grouped FP8 GEMMs of the layer on the 5th-generation tensor cores (tcgen05, accumulators in TMEM, operands by TMA).
+//
+//   kind 0 (GEMM1): act[row, j] = bf16( silu(g) * u * w_route ),  g = acc_gate * (sx[row] * s1[j]),  u likewise with
+//                   weight row I + j; also the per-row amax of the bf16 values.  Replaces
+//                   deep_gemm/include/deep_gemm/impls/mega_moe_dcu_tiles.cuh:380-670 (compute_route_mmac_mtile16_l1_chunk).
+//   kind 1 (GEMM2): out[row, h] = bf16( acc * (s2[row] * sw2[h]) ) stored straight into combine[slot][token][:] of the
+//                   SOURCE rank over NVLink.  Replaces impls/mega_moe_dcu_tiles.cuh:735-1163.
+//
+// One persistent CTA per SM, 192 threads: warp 0 = TMA producer, warp 1 = MMA issuer (owns TMEM), warps 2-5 = epilogue.
+// Tile = 128 pool rows (UMMA M, TMEM lanes) x 256 weight rows (UMMA N, TMEM columns) x 128 bytes of K per stage;
+// two accumulator buffers (2 x 256 TMEM columns) so the epilogue of tile i overlaps the MMAs of tile i+1.
+// For kind 0 the 256 weight rows are 128 gate rows and the 128 matching up rows, so one tile yields 128 SwiGLU outputs.
+#pragma once
+#include <cuda_bf16.h>
+#include "layout.h"
+#include "ptx.cuh"
+
+namespace mm {
+
+constexpr int kBlockM = MM_BLOCK_M;   // 128
+constexpr int kBlockN = 256;
+constexpr int kBlockK = 128;          // bytes == fp8 elements; one 128-byte swizzle atom
+constexpr int kStages = 4;
+constexpr int kGemmThreads = 192;
+constexpr int kABytes = kBlockM * kBlockK;              // 16 KiB
+constexpr int kBBytes = kBlockN * kBlockK;              // 32 KiB
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kStagingRowBytes = 128 + 16;              // one 128-byte output segment per row + pad (bank spread)
+constexpr int kStagingBytes = 4 * 32 * kStagingRowBytes;
+constexpr int kScaleBytes = 2 * kBlockN * 4;
+constexpr int kGemmSmemBytes = 1024 /*align slack*/ + kStages * kStageBytes + kStagingBytes + kScaleBytes + 256 /*barriers*/;
+
+struct GemmParams {
+    int kdim;                  // reduction length (H for kind 0, I for kind 1)
+    int n_blocks;              // tiles along the weight rows (I/128 for kind 0, ceil(H/256) for kind 1)
+    int n_out;                 // I (kind 0) or H (kind 1): valid output columns
+    int w_rows_per_expert;     // 2I (kind 0) or H (kind 1)
+    const int* plan;           // [0] = number of m-blocks in use
+    const int* mblock_expert;
+    const int* mblock_valid;
+    const MmPoolMeta* meta;    // per pool row
+    const float* w_scale;      // [E_loc][w_rows_per_expert]
+    // kind 0
+    __nv_bfloat16* act_bf16;   // [pool_rows][I]
+    unsigned int* row_amax;
+    float clamp;               // +inf = none
+    // kind 1
+    const float* act_scale;    // [pool_rows]
+    uint64_t peers[MM_MAX_RANKS];
+    int64_t combine_off;
+    int T, H;
+    // error reporting
+    int* status;               // MmStatus*
+    uint64_t timeout_ns;
+};
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int kKind>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    // layout: [stages x (A | B)] [staging] [scales] [barriers]
+    const uint32_t staging_u32 = smem_base + kStages * kStageBytes;
+    uint8_t* staging_gen = smem_gen + kStages * kStageBytes;
+    float* scales_gen = reinterpret_cast<float*>(staging_gen + kStagingBytes);
+    const uint32_t bars = staging_u32 + kStagingBytes + kScaleBytes;
+    // barrier slots (8 bytes each): full[kStages], empty[kStages], tmem_full[2], tmem_empty[2]
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (kStages + s); };
+    auto tfull_bar = [&](int a) { return bars + 8u * (2 * kStages + a); };
+    auto tempty_bar = [&](int a) { return bars + 8u * (2 * kStages + 2 + a); };
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + kStages * kStageBytes + kStagingBytes + kScaleBytes + 8 * (2 * kStages + 4));
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + kStages * kStageBytes + kStagingBytes + kScaleBytes + 8 * (2 * kStages + 4) + 8);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 4); }
+        *abort_flag = 0;
+        fence_barrier_init();
+        prefetch_tensormap(&tm_a);
+        prefetch_tensormap(&tm_b);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_slot), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int num_mblocks = p.plan[0];
+    const int num_tiles = num_mblocks * p.n_blocks;
+    const int k_blocks = p.kdim / kBlockK;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        int stage = 0; uint32_t phase = 0;
+        bool alive = true;
+        for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
+            const int mb = tile / p.n_blocks, nb = tile - mb * p.n_blocks;
+            const int e = p.mblock_expert[mb];
+            const int a_row = mb * kBlockM;
+            int b_row0, b_row1;
+            if (kKind == 0) {
+                b_row0 = e * p.w_rows_per_expert + nb * 128;          // gate rows
+                b_row1 = b_row0 + p.w_rows_per_expert / 2;            // matching up rows
+            } else {
+                b_row0 = e * p.w_rows_per_expert + nb * kBlockN;
+                b_row1 = b_row0 + 128;
+            }
+            for (int kb = 0; kb < k_blocks; ++kb) {
+                if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.timeout_ns)) { alive = false; break; }
+                if (lane == 0) {
+                    const uint32_t a_dst = smem_base + stage * kStageBytes;
+                    const uint32_t b_dst = a_dst + kABytes;
+                    mbar_arrive_expect_tx(full_bar(stage), kStageBytes);
+                    tma_load_2d(a_dst, &tm_a, kb * kBlockK, a_row, full_bar(stage));
+                    tma_load_2d(b_dst, &tm_b, kb * kBlockK, b_row0, full_bar(stage));
+                    tma_load_2d(b_dst + 128 * kBlockK, &tm_b, kb * kBlockK, b_row1, full_bar(stage));
+                }
+                __syncwarp();
+                if (++stage == kStages) { stage = 0; phase ^= 1u; }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        constexpr uint32_t idesc = umma_idesc_f8(kBlockM, kBlockN);
+        int stage = 0; uint32_t phase = 0;
+        int acc = 0; uint32_t acc_phase = 0;
+        bool alive = true;
+        for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
+            if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.timeout_ns)) { alive = false; break; }
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + acc * kBlockN;
+            for (int kb = 0; kb < k_blocks; ++kb) {
+                if (!mbar_wait(full_bar(stage), phase, abort_flag, p.timeout_ns)) { alive = false; break; }
+                tc_fence_after();
+                if (lane == 0) {
+                    const uint32_t a_src = smem_base + stage * kStageBytes;
+                    const uint64_t da = umma_desc_k_sw128(a_src);
+                    const uint64_t db = umma_desc_k_sw128(a_src + kABytes);
+#pragma unroll
+                    for (int k = 0; k < kBlockK / 32; ++k) {
+                        // advance 32 bytes of K inside the swizzle atom: +2 in the (address >> 4) field
+                        umma_f8(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(empty_bar(stage));            // smem stage is free once these MMAs retire
+                    if (kb == k_blocks - 1) umma_commit(tfull_bar(acc));   // accumulator complete
+                }
+                __syncwarp();
+                if (++stage == kStages) { stage = 0; phase ^= 1u; }
+            }
+            if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (warps 2..5)
+        const int q = warp & 3;                       // TMEM lane quarter this warp may read
+        const int et = q * 32 + lane;                 // row of the tile == TMEM lane
+        uint8_t* my_staging = staging_gen + (warp - 2) * 32 * kStagingRowBytes;
+        int acc = 0; uint32_t acc_phase = 0;
+        bool alive = true;
+        for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
+            const int mb = tile / p.n_blocks, nb = tile - mb * p.n_blocks;
+            const int e = p.mblock_expert[mb];
+            const int valid = p.mblock_valid[mb];
+            const int row = mb * kBlockM + et;
+            const bool row_ok = et < valid;
+            float* sc = scales_gen + acc * kBlockN;
+            // stage the 256 per-column weight scales of this tile (threads 0..127 of the epilogue, two each)
+            {
+                const int t = (warp - 2) * 32 + lane;
+                const float* ws = p.w_scale + static_cast<int64_t>(e) * p.w_rows_per_expert;
+                if (kKind == 0) {
+                    sc[t] = ws[nb * 128 + t];
+                    sc[128 + t] = ws[p.w_rows_per_expert / 2 + nb * 128 + t];
+                } else {
+                    const int c0 = nb * kBlockN + t, c1 = c0 + 128;
+                    sc[t] = c0 < p.n_out ? ws[c0] : 0.0f;
+                    sc[128 + t] = c1 < p.n_out ? ws[c1] : 0.0f;
+                }
+            }
+            named_bar_sync(1, 128);
+            float row_scale = 0.0f, route_w = 0.0f;
+            uint8_t* out_ptr = nullptr;                // kind 1: destination row in the source rank's combine buffer
+            if (row_ok) {
+                const MmPoolMeta m = p.meta[row];
+                if (kKind == 0) {
+                    row_scale = m.x_scale;
+                    route_w = m.route_weight;
+                } else {
+                    row_scale = p.act_scale[row];
+                    const int src_rank = m.src_info >> 8, slot = m.src_info & 0xff;
+                    out_ptr = reinterpret_cast<uint8_t*>(p.peers[src_rank]) + p.combine_off +
+                              (static_cast<int64_t>(slot) * p.T + m.src_token) * p.H * 2;
+                }
+            }
+            if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.timeout_ns)) { alive = false; break; }
+            tc_fence_after();
+            const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * kBlockN;
+            float amax = 0.0f;
+            if (kKind == 0) {
+                // 128 outputs per row, in 4 chunks of 32; two chunks fill one 128-byte staging segment
+#pragma unroll 1
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t g[32], u[32];
+                    tmem_ld_32x32(t_addr + c * 32, g);
+                    tmem_ld_32x32(t_addr + 128 + c * 32, u);
+                    tmem_ld_wait();
+                    uint32_t packed[16];
+#pragma unroll
+                    for (int j = 0; j < 32; j += 2) {
+                        float o[2];
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            float gv = __uint_as_float(g[j + h]) * (row_scale * sc[c * 32 + j + h]);
+                            float uv = __uint_as_float(u[j + h]) * (row_scale * sc[128 + c * 32 + j + h]);
+                            gv = fminf(fmaxf(gv, -p.clamp), p.clamp);
+                            uv = fminf(fmaxf(uv, -p.clamp), p.clamp);
+                            o[h] = silu_f(gv) * uv * route_w;
+                        }
+                        const uint32_t pk = pack_bf16x2(o[0], o[1]);
+                        packed[j / 2] = pk;
+                        amax = fmaxf(amax, fmaxf(fabsf(__uint_as_float(pk << 16)), fabsf(__uint_as_float(pk & 0xffff0000u))));
+                    }
+                    uint4* dst = reinterpret_cast<uint4*>(my_staging + lane * kStagingRowBytes + (c & 1) * 64);
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) dst[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+                    if (c & 1) {
+                        __syncwarp();
+                        // coalesced flush: 8 lanes cover one row's 128-byte segment
+#pragma unroll
+                        for (int it = 0; it < 8; ++it) {
+                            const int r = it * 4 + (lane >> 3), seg = lane & 7;
+                            if (q * 32 + r < valid) {
+                                const uint4 v = *reinterpret_cast<const uint4*>(my_staging + r * kStagingRowBytes + seg * 16);
+                                uint8_t* o = reinterpret_cast<uint8_t*>(p.act_bf16) +
+                                             (static_cast<int64_t>(mb * kBlockM + q * 32 + r) * p.n_out + nb * 128 + (c >> 1) * 64) * 2 + seg * 16;
+                                *reinterpret_cast<uint4*>(o) = v;
+                            }
+                        }
+                        __syncwarp();
+                    }
+                }
+                if (row_ok) atomicMax(p.row_amax + row, __float_as_uint(amax));
+            } else {
+#pragma unroll 1
+                for (int c = 0; c < 8; ++c) {
+                    uint32_t a[32];
+                    tmem_ld_32x32(t_addr + c * 32, a);
+                    tmem_ld_wait();
+                    uint32_t packed[16];
+#pragma unroll
+                    for (int j = 0; j < 32; j += 2) {
+                        const float o0 = __uint_as_float(a[j]) * (row_scale * sc[c * 32 + j]);
+                        const float o1 = __uint_as_float(a[j + 1]) * (row_scale * sc[c * 32 + j + 1]);
+                        packed[j / 2] = pack_bf16x2(o0, o1);
+                    }
+                    uint4* dst = reinterpret_cast<uint4*>(my_staging + lane * kStagingRowBytes + (c & 1) * 64);
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) dst[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+                    if (c & 1) {
+                        __syncwarp();
+                        const int col0 = nb * kBlockN + (c >> 1) * 64;     // first output column of this segment
+#pragma unroll
+                        for (int it = 0; it < 8; ++it) {
+                            const int r = it * 4 + (lane >> 3), seg = lane & 7;
+                            const uint64_t rp = __shfl_sync(0xffffffffu, reinterpret_cast<uint64_t>(out_ptr), r);
+                            if (rp != 0 && col0 < p.n_out) {
+                                const uint4 v = *reinterpret_cast<const uint4*>(my_staging + r * kStagingRowBytes + seg * 16);
+                                *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(rp) + static_cast<int64_t>(col0) * 2 + seg * 16) = v;
+                            }
+                        }
+                        __syncwarp();
+                    }
+                }
+            }
+            // accumulator buffer may be overwritten by the MMA warp
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar(acc));
+            if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+        }
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    if (*abort_flag != 0) {
+        // a bounded wait expired: give copies that may still be in flight time to land, then report
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 1000000ull) __nanosleep(1000);
+        if (threadIdx.x == 0 && atomicCAS(p.status, 0, MM_ERR_PIPE_TIMEOUT) == 0) {
+            p.status[1] = kKind; p.status[2] = blockIdx.x; p.status[3] = num_tiles; p.status[4] = 0;
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+}  // namespace mm

@@ -1,0 +1,125 @@
+// HBM-bound elementwise stages: per-token FP8 quantisation, activation requantisation, top-k combine reduce.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include "layout.h"
+#include "ptx.cuh"
+
+namespace mm {
+
+__device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
+
+__device__ __forceinline__ uint32_t pack4_e4m3(float a, float b, float c, float d) {
+    const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+    const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+    return lo | (hi << 16);
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Per-row FP8 quantisation, bit-exact with megamoe/__init__.py:51-56 (cast_to_fp8_channelwise):
+//   scale = max(amax|x|, 1e-4) / 448 ; q = e4m3_rne(float(x) / scale)   (true IEEE divisions, as torch does).
+// One warp per row; k % 8 == 0.  The second pass re-reads the row (L1/L2 hit).
+__global__ void __launch_bounds__(256) quant_per_token_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int k,
+                                                             uint8_t* __restrict__ q, float* __restrict__ scale) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const int64_t nwarps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+    const int vecs = k / 8;
+    for (int64_t r = warp; r < rows; r += nwarps) {
+        const uint4* src = reinterpret_cast<const uint4*>(x + r * k);
+        float amax = 0.0f;
+        for (int v = lane; v < vecs; v += 32) {
+            const uint4 d = src[v];
+            const uint32_t w[4] = {d.x, d.y, d.z, d.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) amax = fmaxf(amax, fmaxf(fabsf(bf16_lo(w[i])), fabsf(bf16_hi(w[i]))));
+        }
+        amax = warp_max(amax);
+        const float s = __fdiv_rn(fmaxf(amax, 1.0e-4f), 448.0f);
+        if (lane == 0) scale[r] = s;
+        uint2* dst = reinterpret_cast<uint2*>(q + r * k);
+        for (int v = lane; v < vecs; v += 32) {
+            const uint4 d = src[v];
+            uint2 o;
+            o.x = pack4_e4m3(__fdiv_rn(bf16_lo(d.x), s), __fdiv_rn(bf16_hi(d.x), s), __fdiv_rn(bf16_lo(d.y), s), __fdiv_rn(bf16_hi(d.y), s));
+            o.y = pack4_e4m3(__fdiv_rn(bf16_lo(d.z), s), __fdiv_rn(bf16_hi(d.z), s), __fdiv_rn(bf16_lo(d.w), s), __fdiv_rn(bf16_hi(d.w), s));
+            dst[v] = o;
+        }
+    }
+}
+
+// Activation requantisation after GEMM1 (deep_gemm/include/deep_gemm/impls/mega_moe_dcu_tiles.cuh:672-733):
+//   s2 = max(amax / 448, 1e-4) ; aq = e4m3(a * (1 / s2)).  The row amax was accumulated by the GEMM1 epilogue
+// (atomicMax on the bit pattern); it is reset here so the next call starts from zero.
+// One warp per pool row; padding rows of an m-block are skipped.
+__global__ void __launch_bounds__(256) requant_kernel(const __nv_bfloat16* __restrict__ act, int inter,
+                                                     const int* __restrict__ plan, const int* __restrict__ mblock_valid,
+                                                     unsigned int* __restrict__ row_amax, float* __restrict__ act_scale,
+                                                     uint8_t* __restrict__ act_q) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const int64_t nwarps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+    const int64_t rows = plan[1];
+    const int vecs = inter / 8;
+    for (int64_t r = warp; r < rows; r += nwarps) {
+        if ((r & (MM_BLOCK_M - 1)) >= mblock_valid[r / MM_BLOCK_M]) continue;
+        const float amax = __uint_as_float(row_amax[r]);
+        __syncwarp();
+        if (lane == 0) row_amax[r] = 0u;
+        const float s = fmaxf(__fdiv_rn(amax, 448.0f), 1.0e-4f);
+        const float inv = __fdiv_rn(1.0f, s);
+        if (lane == 0) act_scale[r] = s;
+        const uint4* src = reinterpret_cast<const uint4*>(act + r * inter);
+        uint2* dst = reinterpret_cast<uint2*>(act_q + r * inter);
+        for (int v = lane; v < vecs; v += 32) {
+            const uint4 d = src[v];
+            uint2 o;
+            o.x = pack4_e4m3(bf16_lo(d.x) * inv, bf16_hi(d.x) * inv, bf16_lo(d.y) * inv, bf16_hi(d.y) * inv);
+            o.y = pack4_e4m3(bf16_lo(d.z) * inv, bf16_hi(d.z) * inv, bf16_lo(d.w) * inv, bf16_hi(d.w) * inv);
+            dst[v] = o;
+        }
+    }
+}
+
+// Top-k combine (deep_gemm/include/deep_gemm/impls/mega_moe_dcu.cuh:706-760):
+//   y[t, :] = bf16( sum_{s=0..K-1} f32(combine[s][t][:]) ) in slot order; slots of invalid routes contribute zero.
+// The reference zeroes those slots during its route scan; here they are skipped using the same validity rule.
+__global__ void __launch_bounds__(256) combine_reduce_kernel(const uint8_t* __restrict__ sym, MmSymLayout sl, int E, int T, int K, int H,
+                                                            int num_tokens, const int* __restrict__ runtime_num_tokens,
+                                                            __nv_bfloat16* __restrict__ y) {
+    int n = runtime_num_tokens ? *runtime_num_tokens : num_tokens;
+    n = min(max(n, 0), T);
+    const int vecs = H / 8;
+    const int64_t total = static_cast<int64_t>(n) * vecs;
+    const int64_t* topk_idx = reinterpret_cast<const int64_t*>(sym + sl.topk_idx);
+    const float* topk_w = reinterpret_cast<const float*>(sym + sl.topk_weights);
+    const uint4* comb = reinterpret_cast<const uint4*>(sym + sl.combine);
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int t = static_cast<int>(i / vecs), v = static_cast<int>(i - static_cast<int64_t>(t) * vecs);
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int s = 0; s < K; ++s) {
+            const int64_t e = topk_idx[static_cast<int64_t>(t) * K + s];
+            const float w = topk_w[static_cast<int64_t>(t) * K + s];
+            if (!(e >= 0 && e < E && w != 0.0f)) continue;
+            const uint4 d = comb[(static_cast<int64_t>(s) * T + t) * vecs + v];
+            acc[0] += bf16_lo(d.x); acc[1] += bf16_hi(d.x); acc[2] += bf16_lo(d.y); acc[3] += bf16_hi(d.y);
+            acc[4] += bf16_lo(d.z); acc[5] += bf16_hi(d.z); acc[6] += bf16_lo(d.w); acc[7] += bf16_hi(d.w);
+        }
+        uint4 o;
+        __nv_bfloat162 b;
+        b = __floats2bfloat162_rn(acc[0], acc[1]); o.x = *reinterpret_cast<uint32_t*>(&b);
+        b = __floats2bfloat162_rn(acc[2], acc[3]); o.y = *reinterpret_cast<uint32_t*>(&b);
+        b = __floats2bfloat162_rn(acc[4], acc[5]); o.z = *reinterpret_cast<uint32_t*>(&b);
+        b = __floats2bfloat162_rn(acc[6], acc[7]); o.w = *reinterpret_cast<uint32_t*>(&b);
+        reinterpret_cast<uint4*>(y)[i] = o;
+    }
+}
+
+}  // namespace mm

@@ -1,0 +1,238 @@
+// Routing and dispatch: per-expert histogram, count exchange, deterministic slot assignment, NVLink push.
+//
+// Replaces the reference's route scan + tile build + dispatch pull
+// (deep_gemm/include/deep_gemm/impls/mega_moe_dcu.cuh:335-537, impls/mega_moe_dcu_task.cuh:55-150).  Differences:
+//   * every rank scans only ITS OWN topk_idx and pushes rows to the owner (the reference scans all ranks' routes on
+//     every rank and pulls);
+//   * slots are a pure function of the inputs: an expert's rows are ordered by (source rank, token, top-k slot), the
+//     reference leaves the order to atomicAdd (impls/mega_moe_dcu.cuh:359).
+// Route validity is the reference's rule: 0 <= expert < E and weight != 0 (impls/mega_moe_dcu.cuh:350-354).
+#pragma once
+#include "layout.h"
+#include "ptx.cuh"
+
+namespace mm {
+
+struct RouteParams {
+    uint8_t* sym;            // local symmetric buffer
+    uint8_t* scratch;        // local scratch
+    uint64_t peers[MM_MAX_RANKS];
+    MmSymLayout sl;
+    MmScratchLayout cl;
+    int rank, R, E, E_loc, T, K, H;
+    int num_tokens;                  // host-side token count (ignored when runtime_num_tokens != nullptr)
+    const int* runtime_num_tokens;   // device-side token count (graph mode) or nullptr
+    int* stats;                      // cumulative_local_expert_recv_stats or nullptr
+    uint64_t barrier_timeout_ns;
+};
+
+__device__ __forceinline__ int route_num_tokens(const RouteParams& p) {
+    int n = p.runtime_num_tokens ? *p.runtime_num_tokens : p.num_tokens;
+    return min(max(n, 0), p.T);
+}
+
+__device__ __forceinline__ void report_status(uint8_t* scratch, const MmScratchLayout& cl, int code, int phase, int rank,
+                                              int expected, int observed) {
+    MmStatus* st = reinterpret_cast<MmStatus*>(scratch + cl.status);
+    if (atomicCAS(&st->code, 0, code) == 0) {
+        st->phase = phase; st->rank = rank; st->expected = expected; st->observed = observed;
+    }
+}
+
+// ---- 1. per-block histogram of valid routes ------------------------------------------------------------------
+// grid = route_blocks, block = MM_ROUTE_CHUNK threads; thread i of block b owns route b*CHUNK + i (token-major).
+__global__ void __launch_bounds__(MM_ROUTE_CHUNK) route_count_kernel(RouteParams p) {
+    __shared__ int hist[MM_MAX_EXPERTS];
+    const int n_routes = route_num_tokens(p) * p.K;
+    for (int e = threadIdx.x; e < p.E; e += blockDim.x) hist[e] = 0;
+    __syncthreads();
+    const int route = blockIdx.x * MM_ROUTE_CHUNK + threadIdx.x;
+    if (route < n_routes) {
+        const int64_t e = reinterpret_cast<const int64_t*>(p.sym + p.sl.topk_idx)[route];
+        const float w = reinterpret_cast<const float*>(p.sym + p.sl.topk_weights)[route];
+        if (e >= 0 && e < p.E && w != 0.0f) atomicAdd(&hist[static_cast<int>(e)], 1);
+    }
+    __syncthreads();
+    int* bc = reinterpret_cast<int*>(p.scratch + p.cl.block_counts) + static_cast<int64_t>(blockIdx.x) * p.E;
+    for (int e = threadIdx.x; e < p.E; e += blockDim.x) bc[e] = hist[e];
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        int* epoch = reinterpret_cast<int*>(p.scratch + p.cl.epoch);
+        epoch[0] = epoch[0] + 1;   // one epoch per layer call; later kernels of the call read it
+    }
+}
+
+// ---- 2. prefix over blocks, publish this rank's count vector to every rank -------------------------------------
+// grid = 1, block = 1024.
+__global__ void __launch_bounds__(1024) route_exchange_kernel(RouteParams p) {
+    const int route_blocks = static_cast<int>(p.cl.route_blocks);
+    int* bc = reinterpret_cast<int*>(p.scratch + p.cl.block_counts);
+    for (int e = threadIdx.x; e < p.E; e += blockDim.x) {
+        int run = 0;
+        for (int b = 0; b < route_blocks; ++b) {
+            const int c = bc[static_cast<int64_t>(b) * p.E + e];
+            bc[static_cast<int64_t>(b) * p.E + e] = run;     // exclusive prefix: rows of earlier blocks
+            run += c;
+        }
+        for (int r = 0; r < p.R; ++r) {
+            int* cm = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(p.peers[r]) + p.sl.count_matrix);
+            cm[static_cast<int64_t>(p.rank) * p.E + e] = run;
+        }
+    }
+    if (p.R > 1) {
+        __threadfence_system();
+        __syncthreads();
+        const int epoch = reinterpret_cast<const int*>(p.scratch + p.cl.epoch)[0];
+        if (threadIdx.x < p.R) {
+            int* sig = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(p.peers[threadIdx.x]) + p.sl.signals);
+            st_release_sys(sig + MM_BAR_COUNTS * MM_MAX_RANKS + p.rank, epoch);
+        }
+    }
+}
+
+// Bounded wait until every rank has published `epoch` on barrier `bar` of the LOCAL signal block.
+// Called by the first R threads of a block; returns false on timeout (status recorded).
+__device__ __forceinline__ bool wait_rank_signals(const RouteParams& p, int bar, int epoch) {
+    bool ok = true;
+    if (threadIdx.x < p.R) {
+        const int* sig = reinterpret_cast<const int*>(p.sym + p.sl.signals) + bar * MM_MAX_RANKS + threadIdx.x;
+        const uint64_t t0 = global_timer_ns();
+        int v;
+        while ((v = ld_acquire_sys(sig)) - epoch < 0) {
+            if (global_timer_ns() - t0 > p.barrier_timeout_ns) {
+                report_status(p.scratch, p.cl, MM_ERR_RANK_BARRIER_TIMEOUT, bar, threadIdx.x, epoch, v);
+                ok = false;
+                break;
+            }
+            __nanosleep(100);
+        }
+    }
+    return ok;
+}
+
+// ---- 3. plan: totals, pool offsets, m-block table, destination bases ------------------------------------------
+// grid = 1, block = 1024.  Waits (bounded) for all ranks' count vectors when R > 1.
+__global__ void __launch_bounds__(1024) route_plan_kernel(RouteParams p) {
+    __shared__ int tot[MM_MAX_EXPERTS];
+    __shared__ int before[MM_MAX_EXPERTS];
+    __shared__ int off[MM_MAX_EXPERTS];
+    if (p.R > 1) {
+        const int epoch = reinterpret_cast<const int*>(p.scratch + p.cl.epoch)[0];
+        wait_rank_signals(p, MM_BAR_COUNTS, epoch);
+        __syncthreads();
+    }
+    const int* cm = reinterpret_cast<const int*>(p.sym + p.sl.count_matrix);
+    for (int e = threadIdx.x; e < p.E; e += blockDim.x) {
+        int t = 0, b = 0;
+        for (int r = 0; r < p.R; ++r) {
+            const int c = cm[static_cast<int64_t>(r) * p.E + e];
+            if (r < p.rank) b += c;
+            t += c;
+        }
+        tot[e] = t;
+        before[e] = b;
+    }
+    __syncthreads();
+    if (threadIdx.x < p.R) {   // one thread per owner: exclusive prefix of padded totals over its experts
+        int run = 0;
+        for (int le = 0; le < p.E_loc; ++le) {
+            const int e = threadIdx.x * p.E_loc + le;
+            off[e] = run;
+            run += (tot[e] + MM_BLOCK_M - 1) / MM_BLOCK_M * MM_BLOCK_M;
+        }
+        if (threadIdx.x == p.rank) {
+            int* plan = reinterpret_cast<int*>(p.scratch + p.cl.plan);
+            plan[0] = run / MM_BLOCK_M;
+            plan[1] = run;
+            if (run > p.sl.pool_rows) report_status(p.scratch, p.cl, MM_ERR_POOL_OVERFLOW, 0, p.rank, (int)p.sl.pool_rows, run);
+        }
+    }
+    __syncthreads();
+    int* dest_base = reinterpret_cast<int*>(p.scratch + p.cl.dest_base);
+    for (int e = threadIdx.x; e < p.E; e += blockDim.x) dest_base[e] = off[e] + before[e];
+    int* e_tot = reinterpret_cast<int*>(p.scratch + p.cl.expert_total);
+    int* e_off = reinterpret_cast<int*>(p.scratch + p.cl.expert_off);
+    int* mb_e = reinterpret_cast<int*>(p.scratch + p.cl.mblock_expert);
+    int* mb_v = reinterpret_cast<int*>(p.scratch + p.cl.mblock_valid);
+    for (int le = threadIdx.x; le < p.E_loc; le += blockDim.x) {
+        const int e = p.rank * p.E_loc + le;
+        const int t = tot[e], o = off[e];
+        e_tot[le] = t;
+        e_off[le] = o;
+        if (p.stats) p.stats[le] += t;
+        for (int m = 0; m * MM_BLOCK_M < t; ++m) {
+            mb_e[o / MM_BLOCK_M + m] = le;
+            mb_v[o / MM_BLOCK_M + m] = min(MM_BLOCK_M, t - m * MM_BLOCK_M);
+        }
+    }
+}
+
+// ---- 4. slot assignment + push -----------------------------------------------------------------------------------
+// grid = route_blocks, block = MM_ROUTE_CHUNK.  Thread i owns route b*CHUNK+i; its pool row on the owner is
+//   dest_base[e] + (rows of earlier blocks for e) + (earlier routes of this block with the same e).
+// Then each warp copies its 32 routes' rows (H bytes of fp8 + 16 bytes of metadata) to the owners' pools.
+__global__ void __launch_bounds__(MM_ROUTE_CHUNK) dispatch_kernel(RouteParams p) {
+    __shared__ int s_e[MM_ROUTE_CHUNK];
+    __shared__ int s_row[MM_ROUTE_CHUNK];
+    const int n_routes = route_num_tokens(p) * p.K;
+    const int route = blockIdx.x * MM_ROUTE_CHUNK + threadIdx.x;
+    int e = -1;
+    float w = 0.0f;
+    if (route < n_routes) {
+        const int64_t e64 = reinterpret_cast<const int64_t*>(p.sym + p.sl.topk_idx)[route];
+        w = reinterpret_cast<const float*>(p.sym + p.sl.topk_weights)[route];
+        if (e64 >= 0 && e64 < p.E && w != 0.0f) e = static_cast<int>(e64);
+    }
+    s_e[threadIdx.x] = e;
+    __syncthreads();
+    int row = -1;
+    if (e >= 0) {
+        int within = 0;
+        for (int j = 0; j < static_cast<int>(threadIdx.x); ++j) within += (s_e[j] == e);
+        const int* bc = reinterpret_cast<const int*>(p.scratch + p.cl.block_counts) + static_cast<int64_t>(blockIdx.x) * p.E;
+        row = reinterpret_cast<const int*>(p.scratch + p.cl.dest_base)[e] + bc[e] + within;
+        if (row >= p.sl.pool_rows) row = -1;   // cannot happen with worst-case sizing; never write out of bounds
+    }
+    s_row[threadIdx.x] = row;
+    if (route < n_routes) reinterpret_cast<int*>(p.scratch + p.cl.dest_row)[route] = row;
+    __syncthreads();
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint8_t* x = p.sym + p.sl.x;
+    const float* x_sf = reinterpret_cast<const float*>(p.sym + p.sl.x_sf);
+    const float* tw = reinterpret_cast<const float*>(p.sym + p.sl.topk_weights);
+    for (int i = 0; i < 32; ++i) {
+        const int li = warp * 32 + i;
+        const int r_row = s_row[li];
+        if (r_row < 0) continue;
+        const int r_e = s_e[li];
+        const int r_route = blockIdx.x * MM_ROUTE_CHUNK + li;
+        const int token = r_route / p.K, slot = r_route - token * p.K;
+        uint8_t* peer = reinterpret_cast<uint8_t*>(p.peers[r_e / p.E_loc]);
+        const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<int64_t>(token) * p.H);
+        uint4* dst = reinterpret_cast<uint4*>(peer + p.sl.pool_x + static_cast<int64_t>(r_row) * p.H);
+        for (int v = lane; v < p.H / 16; v += 32) dst[v] = src[v];
+        if (lane == 0) {
+            MmPoolMeta m;
+            m.x_scale = x_sf[token];
+            m.route_weight = tw[r_route];
+            m.src_token = token;
+            m.src_info = (p.rank << 8) | slot;
+            *reinterpret_cast<uint4*>(peer + p.sl.pool_meta + static_cast<int64_t>(r_row) * sizeof(MmPoolMeta)) =
+                *reinterpret_cast<uint4*>(&m);
+        }
+    }
+}
+
+// ---- cross-rank barrier as a kernel of its own (staged path) ---------------------------------------------------
+// grid = 1, block = 32: publish the call epoch on barrier `bar` of every rank, then wait for all ranks.
+__global__ void rank_barrier_kernel(RouteParams p, int bar) {
+    const int epoch = reinterpret_cast<const int*>(p.scratch + p.cl.epoch)[0];
+    __threadfence_system();
+    if (threadIdx.x < p.R) {
+        int* sig = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(p.peers[threadIdx.x]) + p.sl.signals);
+        st_release_sys(sig + bar * MM_MAX_RANKS + p.rank, epoch);
+    }
+    wait_rank_signals(p, bar, epoch);
+}
+
+}  // namespace mm

@@ -1,0 +1,468 @@
+"""B200 (sm_100a) implementation of the `megamoe` Python API of yuguo-Jack/DeepGEMM.
+
+Same public names, argument meaning and error behaviour as the reference package (megamoe/__init__.py:461-473);
+underneath, every step runs as hand-written CUDA in libmegamoe_b200.so, called through its C ABI with raw
+pointers.  There is no CPU or PyTorch fallback: CUDA tensors are required and a missing library is an error.
+
+Differences a caller can observe (all supersets of the reference behaviour):
+  * any EP size in 1..16 and any shape with hidden % 128 == 0, intermediate % 128 == 0, top-k <= 32 is accepted
+    (the reference accepts only EP8 / 256 experts / top-6 / 4096 / 2048: csrc/kernels/mega_moe_fused_hip.cu:94-119);
+  * `transform_fp8_weights_for_mega_moe` returns weights in plain `[E_loc, rows, K]` layout (what TMA wants);
+    weights in the reference's Marlin layout `[E_loc, rows/16, K*16]` are also accepted and un-permuted once;
+  * `group=None` builds a single-rank buffer without torch.distributed;
+  * device-side waits are bounded: `SymmBuffer.check_status()` reports a timeout instead of aborting the process.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+import os
+from types import SimpleNamespace
+from typing import Optional, Tuple
+
+import torch
+
+from .. import _lib
+
+__version__ = "0.1"
+
+_LARGE_OPT_FORCE_VALUES = {"1", "true", "yes", "on", "large_opt", "3stage"}
+_LARGE_OPT_AUTO_VALUES = {"auto", "threshold", "adaptive"}
+_LARGE_OPT_ENV = "MEGAMOE_DCU_USE_LARGE_OPT_3STAGE"
+_LARGE_OPT_THRESHOLD_ENV = "MEGAMOE_DCU_LARGE_OPT_3STAGE_TOKEN_THRESHOLD"
+_LARGE_OPT_DEFAULT_THRESHOLD = 128
+# un-prefixed aliases of the reference's environment variables
+_ALIASES = {_LARGE_OPT_ENV: "MEGAMOE_USE_STAGED", _LARGE_OPT_THRESHOLD_ENV: "MEGAMOE_STAGED_TOKEN_THRESHOLD"}
+
+# the fused single-launch variant is selected for token counts at or below the threshold once it is built in
+_FUSED_AVAILABLE = False
+
+
+def _align(value: int, alignment: int) -> int:
+    return ((value + alignment - 1) // alignment) * alignment
+
+
+def _env(name: str, default: str) -> str:
+    v = os.getenv(name)
+    if v is None and name in _ALIASES:
+        v = os.getenv(_ALIASES[name])
+    return default if v is None else v
+
+
+def _large_opt_3stage_mode() -> str:
+    """megamoe/__init__.py:25-31."""
+    value = _env(_LARGE_OPT_ENV, "auto").strip().lower()
+    if value in _LARGE_OPT_FORCE_VALUES:
+        return "force"
+    if value in _LARGE_OPT_AUTO_VALUES:
+        return "auto"
+    return "off"
+
+
+def _large_opt_3stage_threshold() -> int:
+    return int(_env(_LARGE_OPT_THRESHOLD_ENV, str(_LARGE_OPT_DEFAULT_THRESHOLD)))
+
+
+def _large_opt_3stage_selected(num_tokens: int, mode: str, threshold: int) -> bool:
+    """megamoe/__init__.py:38-43: staged when forced, or in auto mode above the threshold."""
+    if mode == "force":
+        return True
+    if mode == "auto":
+        return num_tokens > threshold
+    return False
+
+
+def _is_current_stream_capturing() -> bool:
+    checker = getattr(torch.cuda, "is_current_stream_capturing", None)
+    return bool(checker()) if checker is not None else False
+
+
+def _stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _require_cuda(t: torch.Tensor, name: str) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor (this package has no CPU path)")
+
+
+# ------------------------------------------------------------------------------------------------ quantisation
+def cast_to_fp8_channelwise(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Per-row FP8 e4m3 cast: scale = clamp(amax,1e-4)/448 (megamoe/__init__.py:51-56), bit-exact, as one kernel."""
+    if x.dim() != 2:
+        raise ValueError("channelwise FP8 cast expects a 2D tensor")
+    _require_cuda(x, "x")
+    if x.dtype != torch.bfloat16:
+        raise TypeError("cast_to_fp8_channelwise expects bfloat16 input")
+    rows, k = x.shape
+    if k % 8 != 0:
+        raise ValueError("the row length must be a multiple of 8")
+    x = x.contiguous()
+    out = torch.empty((rows, k), dtype=torch.float8_e4m3fn, device=x.device)
+    scale = torch.empty((rows,), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib().mm_quant_per_token(x.data_ptr(), rows, k, out.data_ptr(), scale.data_ptr(), _stream_ptr()))
+    return out, scale
+
+
+def cast_grouped_weight_to_fp8_channelwise(weights: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Per output row of every expert (megamoe/__init__.py:59-78)."""
+    if weights.dim() != 3:
+        raise ValueError("MegaMoE grouped weights must be 3D tensors")
+    g, rows, k = weights.shape
+    q, s = cast_to_fp8_channelwise(weights.reshape(g * rows, k))
+    return q.reshape(g, rows, k), s.reshape(g, rows)
+
+
+def weight8bit_nt_kpack2_marlin(weight: torch.Tensor, k_tile: int = 16, n_tile: int = 16) -> torch.Tensor:
+    """The reference's 16x16 tile permutation [E,R,K] -> [E,R/16,K*16] (megamoe/__init__.py:81-98).  Kept so that
+    callers holding Marlin-packed checkpoints interoperate; the B200 kernels themselves read the plain layout."""
+    if weight.dim() != 3:
+        raise ValueError("MegaMoE Marlin weight layout expects a 3D grouped weight tensor")
+    if k_tile != 16 or n_tile != 16:
+        raise ValueError("DCU W8A8 MegaMoE currently supports only 16x16 kpack2 Marlin tiles")
+    g, rows, k = weight.shape
+    if rows % n_tile != 0 or k % k_tile != 0:
+        raise ValueError("DCU W8A8 MegaMoE Marlin weights require rows and K divisible by 16")
+    return (weight.view(torch.uint8).reshape(g, rows // n_tile, n_tile, k // k_tile, k_tile).permute(0, 1, 3, 2, 4)
+            .contiguous().reshape(g, rows // n_tile, k * n_tile).view(weight.dtype))
+
+
+def _marlin_inverse(weight: torch.Tensor, rows: int, k: int) -> torch.Tensor:
+    g = weight.shape[0]
+    return (weight.view(torch.uint8).reshape(g, rows // 16, k // 16, 16, 16).permute(0, 1, 3, 2, 4)
+            .contiguous().reshape(g, rows, k).view(weight.dtype))
+
+
+def transform_fp8_weights_for_mega_moe(l1_weights: torch.Tensor, l2_weights: torch.Tensor, layout: str = "native"):
+    """bf16 [E_loc,2I,H], [E_loc,H,I] -> ((w1_fp8, s1[E_loc,2I]), (w2_fp8, s2[E_loc,H])) (megamoe/__init__.py:280-289).
+    layout="native" keeps [E_loc, rows, K]; layout="marlin" applies the reference's permutation."""
+    l1_fp8, l1_scale = cast_grouped_weight_to_fp8_channelwise(l1_weights)
+    l2_fp8, l2_scale = cast_grouped_weight_to_fp8_channelwise(l2_weights)
+    if layout == "marlin":
+        return (weight8bit_nt_kpack2_marlin(l1_fp8), l1_scale), (weight8bit_nt_kpack2_marlin(l2_fp8), l2_scale)
+    if layout != "native":
+        raise ValueError("layout must be 'native' or 'marlin'")
+    return (l1_fp8, l1_scale), (l2_fp8, l2_scale)
+
+
+def get_mega_moe_hip_build_config() -> dict:
+    """csrc/apis/mega_dcu.hpp:28-39 + megamoe/__init__.py:101-110 (name kept for drop-in use)."""
+    config = _lib.build_config()
+    config["large_opt_3stage_env"] = _LARGE_OPT_ENV
+    config["large_opt_3stage_auto_values"] = sorted(_LARGE_OPT_AUTO_VALUES)
+    config["large_opt_3stage_threshold_env"] = _LARGE_OPT_THRESHOLD_ENV
+    config["large_opt_3stage_default_threshold"] = _LARGE_OPT_DEFAULT_THRESHOLD
+    config["large_opt_3stage_shape"] = "any EP<=16, hidden%128==0, intermediate%128==0, topk<=32"
+    config["cuda_graph_max_tokens_source"] = "requested num_max_tokens_per_rank"
+    config["cuda_graph_execution"] = "explicit_big_fused_or_large_opt_3stage"
+    config["fused_variant_available"] = _FUSED_AVAILABLE
+    return config
+
+
+# ------------------------------------------------------------------------------------------------ symmetric buffer
+class _DeviceMemory:
+    """Exposes a raw device allocation to torch through the CUDA array interface."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|i1", "data": (ptr, False), "version": 3,
+                                         "strides": None}
+
+
+def _view(buffer: torch.Tensor, offset: int, shape, dtype: torch.dtype) -> torch.Tensor:
+    n = int(math.prod(shape)) * torch.empty((), dtype=dtype).element_size()
+    return buffer[offset:offset + n].view(dtype).view(*shape)
+
+
+class SymmBuffer:
+    """Peer-mapped buffer + local scratch of one rank (megamoe/__init__.py:113-249)."""
+
+    def __init__(self, group, num_experts: int, num_max_tokens_per_rank: int, num_topk: int, hidden: int,
+                 intermediate_hidden: int, use_fp8_dispatch: bool = True, activation: str = "swiglu",
+                 cuda_graph_max_tokens_per_rank: Optional[int] = None):
+        if not torch.cuda.is_available():
+            raise RuntimeError("megamoe (B200) needs a CUDA device")
+        if activation != "swiglu":
+            raise ValueError("only swiglu is supported")
+        if not use_fp8_dispatch:
+            raise ValueError("only FP8 dispatch is supported")
+        self.group = group
+        self.num_experts = int(num_experts)
+        self.num_max_tokens_per_rank = int(num_max_tokens_per_rank)
+        self.num_topk = int(num_topk)
+        self.hidden = int(hidden)
+        self.intermediate_hidden = int(intermediate_hidden)
+        self._large_opt_3stage_mode = _large_opt_3stage_mode()
+        self._large_opt_3stage_threshold = _large_opt_3stage_threshold()
+        self.cuda_graph_max_tokens_per_rank = int(cuda_graph_max_tokens_per_rank
+                                                  if cuda_graph_max_tokens_per_rank is not None
+                                                  else num_max_tokens_per_rank)
+        if (self.cuda_graph_max_tokens_per_rank <= 0
+                or self.cuda_graph_max_tokens_per_rank > self.num_max_tokens_per_rank):
+            raise ValueError(f"cuda_graph_max_tokens_per_rank must be in 1..{self.num_max_tokens_per_rank}")
+
+        self.num_ranks = 1 if group is None else group.size()
+        self.rank = 0 if group is None else group.rank()
+        dims = (self.num_ranks, self.num_experts, self.num_max_tokens_per_rank, self.num_topk, self.hidden,
+                self.intermediate_hidden)
+        self._dims = dims
+        self._sym_off, num_bytes = _lib.symm_buffer_layout(*dims)
+        self._scr_off, scratch_bytes = _lib.scratch_layout(*dims)
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        lib = _lib.lib()
+        self._owned_ptr = None
+        self._peer_mapped = []
+        if self.num_ranks == 1:
+            self.buffer = torch.empty((num_bytes,), dtype=torch.int8, device=self.device)
+            buffer_ptr = self.buffer.data_ptr()
+            buffer_ptrs = [buffer_ptr]
+        else:
+            import torch.distributed as dist
+            ptr = ctypes.c_void_p()
+            handle = ctypes.create_string_buffer(64)
+            _lib.check(lib.mm_ipc_alloc(num_bytes, ctypes.byref(ptr), handle))
+            buffer_ptr = int(ptr.value)
+            self._owned_ptr = buffer_ptr
+            self.buffer = torch.as_tensor(_DeviceMemory(buffer_ptr, num_bytes), device=self.device)
+            handles = [None] * self.num_ranks
+            dist.all_gather_object(handles, (self.rank, bytes(handle.raw)), group)
+            buffer_ptrs = [0] * self.num_ranks
+            for r, raw in handles:
+                if r == self.rank:
+                    buffer_ptrs[r] = buffer_ptr
+                else:
+                    peer = ctypes.c_void_p()
+                    _lib.check(lib.mm_ipc_open(ctypes.create_string_buffer(raw, 64), ctypes.byref(peer)))
+                    buffer_ptrs[r] = int(peer.value)
+                    self._peer_mapped.append(int(peer.value))
+        self.route_scratch = torch.empty((scratch_bytes,), dtype=torch.int8, device=self.device)
+        sig = self._sym_off["signals"]
+        self.handle = SimpleNamespace(buffer_ptrs=buffer_ptrs, buffer_ptr=buffer_ptr,
+                                      signal_ptrs=[p + sig for p in buffer_ptrs], signal_buffer_ptr=buffer_ptr + sig)
+        self._peer_array = (ctypes.c_uint64 * _lib.MAX_RANKS)(*buffer_ptrs)
+        self.reset()
+
+        T, K, H = self.num_max_tokens_per_rank, self.num_topk, self.hidden
+        o = self._sym_off
+        self.x = _view(self.buffer, o["x"], (T, H), torch.float8_e4m3fn)
+        self.x_sf = _view(self.buffer, o["x_sf"], (T,), torch.float32)
+        self.topk_idx = _view(self.buffer, o["topk_idx"], (T, K), torch.int64)
+        self.topk_weights = _view(self.buffer, o["topk_weights"], (T, K), torch.float32)
+        empty_fp8 = self.buffer[o["combine"]:o["combine"]].view(torch.float8_e4m3fn)
+        empty_f32 = self.buffer[o["combine"]:o["combine"]].view(torch.float32)
+        self.l1_acts, self.l1_acts_sf, self.l2_acts, self.l2_acts_sf = empty_fp8, empty_f32, empty_fp8, empty_f32
+        self.cuda_graph_num_tokens = _view(self.buffer, o["runtime_num_tokens"], (1,), torch.int32)
+        self.cuda_graph_num_tokens.fill_(self.cuda_graph_max_tokens_per_rank)
+        torch.cuda.synchronize()
+        if group is not None:
+            import torch.distributed as dist
+            dist.barrier(group)
+
+    # -- maintenance ------------------------------------------------------------------------------
+    def reset(self) -> None:
+        """Zero the control regions and (re)write the peer table; collective across the group."""
+        torch.cuda.synchronize()
+        if self.group is not None:
+            import torch.distributed as dist
+            dist.barrier(self.group)
+        _lib.check(_lib.lib().mm_init_buffers(self.buffer.data_ptr(), self.route_scratch.data_ptr(), self._peer_array,
+                                              self.rank, *self._dims, _stream_ptr()))
+        torch.cuda.synchronize()
+        if self.group is not None:
+            import torch.distributed as dist
+            dist.barrier(self.group)
+        if getattr(self, "cuda_graph_num_tokens", None) is not None:
+            self.cuda_graph_num_tokens.fill_(self.cuda_graph_max_tokens_per_rank)
+
+    def check_status(self) -> None:
+        """Synchronise and raise if a bounded device-side wait expired during an earlier call."""
+        out = (ctypes.c_int32 * 5)()
+        _lib.check(_lib.lib().mm_read_status(self.route_scratch.data_ptr(), _stream_ptr(), out))
+        if out[0] != 0:
+            raise _lib.MegaMoeError(
+                f"device status {out[0]} ({_lib.STATUS_NAMES.get(out[0], '?')}): phase={out[1]} rank/block={out[2]} "
+                f"expected={out[3]} observed={out[4]}; call SymmBuffer.reset() on every rank before reuse")
+
+    def scratch_view(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
+        """Typed view of a region of the local scratch buffer (for tests and inspection)."""
+        return _view(self.route_scratch, self._scr_off[name], shape, dtype)
+
+    def symm_view(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
+        return _view(self.buffer, self._sym_off[name], shape, dtype)
+
+    @property
+    def pool_rows(self) -> int:
+        return int(self._sym_off["pool_rows"])
+
+    def destroy(self):
+        if self.handle is not None:
+            torch.cuda.synchronize()
+            lib = _lib.lib()
+            for p in self._peer_mapped:
+                _lib.check(lib.mm_ipc_close(p))
+            self._peer_mapped = []
+            if self.group is not None:
+                import torch.distributed as dist
+                dist.barrier(self.group)
+            self.x = self.x_sf = self.topk_idx = self.topk_weights = None
+            self.l1_acts = self.l1_acts_sf = self.l2_acts = self.l2_acts_sf = None
+            self.cuda_graph_num_tokens = None
+            self.buffer = None
+            if self._owned_ptr is not None:
+                _lib.check(lib.mm_ipc_free(self._owned_ptr))
+                self._owned_ptr = None
+        self.handle = None
+        self.buffer = None
+        self.group = None
+        self.route_scratch = None
+
+
+def get_symm_buffer_for_mega_moe(group, num_experts: int, num_max_tokens_per_rank: int, num_topk: int, hidden: int,
+                                 intermediate_hidden: int, use_fp8_dispatch: bool = True,
+                                 activation: str = "swiglu") -> SymmBuffer:
+    """megamoe/__init__.py:252-277: capacity aligned up to 384 tokens, the request kept as the graph bucket size."""
+    requested = int(num_max_tokens_per_rank)
+    aligned = _align(requested, _lib.lib().mm_token_alignment())
+    return SymmBuffer(group, num_experts, aligned, num_topk, hidden, intermediate_hidden, use_fp8_dispatch, activation,
+                      cuda_graph_max_tokens_per_rank=requested)
+
+
+# ------------------------------------------------------------------------------------------------ the layer
+_native_weight_cache = {}
+
+
+def _native_weight(w: torch.Tensor, rows: int, k: int, what: str) -> torch.Tensor:
+    """Accept [E_loc, rows, K] or the reference's Marlin shape [E_loc, rows/16, K*16] (un-permuted once, cached)."""
+    if w.dim() != 3:
+        raise RuntimeError("weights must be grouped 3D tensors")
+    if w.shape[1] == rows and w.shape[2] == k:
+        return w if w.is_contiguous() else w.contiguous()
+    if w.shape[1] == rows // 16 and w.shape[2] == k * 16:
+        key = (w.data_ptr(), tuple(w.shape), w._version)
+        hit = _native_weight_cache.get(key)
+        if hit is None:
+            if len(_native_weight_cache) > 16:
+                _native_weight_cache.clear()
+            hit = _marlin_inverse(w, rows, k)
+            _native_weight_cache[key] = hit
+        return hit
+    raise RuntimeError(f"invalid {what} weight shape {tuple(w.shape)}, expected [expert, {rows}, {k}] "
+                       f"or Marlin [expert, {rows // 16}, {k * 16}]")
+
+
+def fp8_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer: SymmBuffer,
+                 cumulative_local_expert_recv_stats: Optional[torch.Tensor] = None,
+                 recipe: Tuple[int, int, int] = (1, 1, 32), activation: str = "swiglu",
+                 activation_clamp: Optional[float] = None, fast_math: bool = True, big_fused_cuda_graph: bool = False,
+                 stages_fused_cuda_graph: bool = False, dispatch_num_tokens: Optional[int] = None) -> None:
+    """The W8A8 channelwise Mega MoE layer, in place into `y` (megamoe/__init__.py:328-449 and
+    csrc/apis/mega_dcu.hpp:338-445 for the argument checks).  Inputs are read from the SymmBuffer views
+    x / x_sf / topk_idx / topk_weights; the call is asynchronous on the current stream."""
+    if big_fused_cuda_graph and stages_fused_cuda_graph:
+        raise ValueError("choose only one of big_fused_cuda_graph or stages_fused_cuda_graph")
+    graph_mode = big_fused_cuda_graph or stages_fused_cuda_graph
+    sb = sym_buffer
+    if graph_mode:
+        graph_max_tokens = int(sb.cuda_graph_max_tokens_per_rank)
+        if int(y.size(0)) < graph_max_tokens:
+            raise ValueError(f"CUDA graph mode requires y to have at least {graph_max_tokens} rows; pass a fixed "
+                             "graph-bucket output buffer and consume only the valid prefix")
+        if cumulative_local_expert_recv_stats is not None:
+            raise ValueError("CUDA graph mode does not support cumulative_local_expert_recv_stats")
+        if stages_fused_cuda_graph and sb._large_opt_3stage_mode == "off":
+            raise RuntimeError("stages_fused_cuda_graph=True requires MEGAMOE_DCU_USE_LARGE_OPT_3STAGE=auto or 1")
+        staged = bool(stages_fused_cuda_graph)
+        call_y = y[:graph_max_tokens]
+        runtime_ptr = sb.cuda_graph_num_tokens.data_ptr()
+    else:
+        if _is_current_stream_capturing():
+            raise RuntimeError(
+                "DCU MegaMoE CUDA Graph capture requires an explicit graph mode: pass big_fused_cuda_graph=True for the "
+                "persistent fused path or stages_fused_cuda_graph=True for the staged K1/K2/K3 path. "
+                "Capturing the eager auto-dispatch path is not graph-bucket safe.")
+        dispatch_tokens = int(y.size(0)) if dispatch_num_tokens is None else int(dispatch_num_tokens)
+        if dispatch_tokens < 0 or dispatch_tokens > int(sb.num_max_tokens_per_rank):
+            raise ValueError(f"dispatch_num_tokens must be in 0..{int(sb.num_max_tokens_per_rank)}")
+        staged = _large_opt_3stage_selected(dispatch_tokens, sb._large_opt_3stage_mode, sb._large_opt_3stage_threshold)
+        call_y = y
+        runtime_ptr = None
+    if not _FUSED_AVAILABLE:
+        staged = True
+
+    # argument checks of csrc/apis/mega_dcu.hpp:355-445
+    if tuple(recipe) != (1, 1, 32):
+        raise RuntimeError("DCU W8A8 MegaMoE expects recipe=(1,1,32)")
+    if activation != "swiglu":
+        raise RuntimeError("DCU W8A8 MegaMoE supports swiglu only")
+    if not fast_math:
+        raise RuntimeError("fast_math=False is not supported")
+    _require_cuda(call_y, "y")
+    if call_y.dtype != torch.bfloat16 or call_y.dim() != 2 or not call_y.is_contiguous():
+        raise RuntimeError("y must be a contiguous 2D BF16 tensor")
+    l1_w, l1_sf = l1_weights
+    l2_w, l2_sf = l2_weights
+    if l1_w.dtype != torch.float8_e4m3fn or l2_w.dtype != torch.float8_e4m3fn:
+        raise RuntimeError("DCU MegaMoE expects FP8 E4M3 L1/L2 weights")
+    if l1_sf.dtype != torch.float32 or l2_sf.dtype != torch.float32:
+        raise RuntimeError("DCU MegaMoE expects FP32 channelwise weight scales")
+    if l1_sf.dim() != 2 or l2_sf.dim() != 2:
+        raise RuntimeError("weight scales must be [expert,row]")
+    num_tokens, hidden = int(call_y.size(0)), int(call_y.size(1))
+    if l1_sf.size(1) % 2 != 0:
+        raise RuntimeError("invalid L1 scale shape")
+    inter = int(l1_sf.size(1)) // 2
+    e_loc = int(l1_w.size(0))
+    if hidden != sb.hidden or inter != sb.intermediate_hidden:
+        raise RuntimeError("weights / y do not match the SymmBuffer's hidden sizes")
+    if sb.num_experts != e_loc * sb.num_ranks:
+        raise RuntimeError("invalid expert count")
+    if tuple(l1_sf.shape) != (e_loc, 2 * inter):
+        raise RuntimeError("invalid L1 scale shape")
+    if tuple(l2_sf.shape) != (e_loc, hidden) or int(l2_w.size(0)) != e_loc:
+        raise RuntimeError("invalid L2 scale shape")
+    if num_tokens > sb.num_max_tokens_per_rank:
+        raise RuntimeError("too many tokens")
+    w1 = _native_weight(l1_w, 2 * inter, hidden, "L1")
+    w2 = _native_weight(l2_w, hidden, inter, "L2")
+    stats_ptr = None
+    if cumulative_local_expert_recv_stats is not None:
+        st = cumulative_local_expert_recv_stats
+        if st.dtype != torch.int32:
+            raise RuntimeError("stats must be int32")
+        if st.numel() != e_loc:
+            raise RuntimeError("stats must have num_experts_per_rank elements")
+        _require_cuda(st, "stats")
+        stats_ptr = st.data_ptr()
+    clamp = float("inf") if activation_clamp is None else float(activation_clamp)
+    with torch.cuda.device(sb.device):
+        _lib.check(_lib.lib().mm_fp8_w8a8_mega_moe(
+            call_y.data_ptr(), w1.data_ptr(), l1_sf.contiguous().data_ptr(), w2.data_ptr(), l2_sf.contiguous().data_ptr(),
+            stats_ptr, sb.buffer.data_ptr(), sb.route_scratch.data_ptr(), sb._peer_array, sb.rank, sb.num_ranks,
+            sb.num_max_tokens_per_rank, e_loc, num_tokens, sb.num_topk, hidden, inter, clamp,
+            _lib.MODE_STAGED if staged else _lib.MODE_FUSED, runtime_ptr, _stream_ptr()))
+
+
+fp8_w8a8_mega_moe = fp8_mega_moe
+
+
+def deepep_deepgemm_preprocess_channelwise(*args, **kwargs):
+    raise NotImplementedError("DeepEP-layout pre-processing helpers are not part of this build")
+
+
+def deepep_deepgemm_postprocess_channelwise(*args, **kwargs):
+    raise NotImplementedError("DeepEP-layout post-processing helpers are not part of this build")
+
+
+__all__ = [
+    "SymmBuffer",
+    "cast_to_fp8_channelwise",
+    "cast_grouped_weight_to_fp8_channelwise",
+    "weight8bit_nt_kpack2_marlin",
+    "get_mega_moe_hip_build_config",
+    "get_symm_buffer_for_mega_moe",
+    "transform_fp8_weights_for_mega_moe",
+    "deepep_deepgemm_preprocess_channelwise",
+    "deepep_deepgemm_postprocess_channelwise",
+    "fp8_mega_moe",
+    "fp8_w8a8_mega_moe",
+]

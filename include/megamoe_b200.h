@@ -1,0 +1,102 @@
+/*
+ * C ABI of libmegamoe_b200.so -- the B200 (sm_100a) implementation of the W8A8 channelwise Mega MoE layer.
+ *
+ * These entry points are what a binding of the reference's `megamoe._C` extension module would call for this
+ * path; each comment names the reference interface it replaces (paths relative to the reference project).
+ * Plain pointers and integers only: no torch types, no C++ exceptions.  Every function returns 0 on success
+ * and a non-zero code on failure; mm_last_error() then returns a message (thread-local, valid until the next
+ * call on the same thread).  All device work is enqueued on `stream` (a cudaStream_t passed as void*) and the
+ * call returns without synchronising, unless stated otherwise.
+ */
+#ifndef MEGAMOE_B200_H
+#define MEGAMOE_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MM_ABI_MAX_RANKS 16
+
+/* indices into the `offsets` array filled by mm_symm_buffer_layout */
+enum {
+    MM_SYM_PEER_PTRS = 0, MM_SYM_SIGNALS, MM_SYM_RUNTIME_NUM_TOKENS, MM_SYM_COUNT_MATRIX,
+    MM_SYM_X, MM_SYM_X_SF, MM_SYM_TOPK_IDX, MM_SYM_TOPK_WEIGHTS,
+    MM_SYM_POOL_X, MM_SYM_POOL_META, MM_SYM_COMBINE, MM_SYM_POOL_ROWS, MM_SYM_NUM_OFFSETS
+};
+/* indices into the `offsets` array filled by mm_scratch_layout */
+enum {
+    MM_SCR_STATUS = 0, MM_SCR_EPOCH, MM_SCR_PLAN, MM_SCR_BLOCK_COUNTS, MM_SCR_DEST_BASE, MM_SCR_EXPERT_TOTAL,
+    MM_SCR_EXPERT_OFF, MM_SCR_MBLOCK_EXPERT, MM_SCR_MBLOCK_VALID, MM_SCR_DEST_ROW, MM_SCR_ROW_AMAX,
+    MM_SCR_ACT_SCALE, MM_SCR_ACT_BF16, MM_SCR_ACT_FP8, MM_SCR_ROUTE_BLOCKS, MM_SCR_NUM_OFFSETS
+};
+/* execution variants of mm_fp8_w8a8_mega_moe */
+enum { MM_MODE_STAGED = 0, MM_MODE_FUSED = 1 };
+
+/* Message of the last failure on this thread. */
+const char* mm_last_error(void);
+
+/* Token-count alignment of the symmetric buffer (384).
+ * Replaces get_token_alignment_for_mega_moe, csrc/apis/mega_dcu.hpp:24-26. */
+int mm_token_alignment(void);
+
+/* Byte offsets of every region of the symmetric buffer and its total size.
+ * Replaces get_symm_buffer_size_for_mega_moe and its slice function, csrc/apis/mega_dcu.hpp:93-154.
+ * R ranks, E experts in total, T max tokens per rank, K top-k, H hidden, I intermediate. */
+int mm_symm_buffer_layout(int R, int E, int T, int K, int H, int I, int64_t* offsets, int64_t* total_bytes);
+
+/* Byte offsets of every region of the local (non-symmetric) scratch buffer and its total size.
+ * Replaces get_mega_moe_route_scratch_size_for_mega_moe, csrc/apis/mega_dcu.hpp:156-169. */
+int mm_scratch_layout(int R, int E, int T, int K, int H, int I, int64_t* offsets, int64_t* total_bytes);
+
+/* Peer-mappable device memory: allocate and export / import / unmap / free.  The handle is 64 bytes.
+ * Replace allocate_hip_ipc_buffer, open_hip_ipc_handles, close_hip_ipc_handles, free_hip_ipc_buffer,
+ * csrc/python_api_hip.cpp:38-101.  These calls synchronise. */
+int mm_ipc_alloc(int64_t bytes, void** dev_ptr, void* handle64);
+int mm_ipc_open(const void* handle64, void** dev_ptr);
+int mm_ipc_close(void* dev_ptr);
+int mm_ipc_free(void* dev_ptr);
+
+/* Zero the control regions of both buffers (signals, count matrix, epochs, status, row amax) and write the
+ * peer pointer table into the symmetric buffer header.  Call once after allocation, and again (after a host
+ * barrier across ranks) to recover from a reported error.
+ * Replaces set_mega_moe_peer_ptrs, csrc/apis/mega_dcu.hpp:171-210 (and the buffer.zero_() before it). */
+int mm_init_buffers(void* sym_base, void* scratch, const uint64_t* peer_ptrs, int rank,
+                    int R, int E, int T, int K, int H, int I, void* stream);
+
+/* Per-row FP8 e4m3 quantisation of a bf16 matrix [rows, k] (k % 8 == 0): scale = max(amax,1e-4)/448.
+ * Replaces cast_to_fp8_channelwise, megamoe/__init__.py:51-56 (bit-exact codes and scales). */
+int mm_quant_per_token(const void* x_bf16, int64_t rows, int k, void* out_fp8, float* out_scale, void* stream);
+
+/* The layer.  Inputs x / x_sf / topk_idx / topk_weights are read from the symmetric buffer views; y receives
+ * bf16 [num_tokens, H].  w1 fp8 [E_loc, 2I, H] with s1 f32 [E_loc, 2I] (rows [0,I) gate, [I,2I) up); w2 fp8
+ * [E_loc, H, I] with s2 f32 [E_loc, H].  stats (nullable) int32 [E_loc] accumulates rows received per local
+ * expert.  peer_ptrs: HOST array of the R ranks' symmetric-buffer device addresses (entry `rank` is sym_base).
+ * runtime_num_tokens (nullable): device int32 overriding num_tokens (CUDA-graph bucket mode).
+ * activation_clamp: +inf for none.  mode: MM_MODE_STAGED or MM_MODE_FUSED.
+ * Replaces launch_mega_moe_multirank_persistent_hip_w8a8_channelwise, csrc/apis/mega_dcu.hpp:41-55, and the
+ * staged driver fp8_mega_moe_large_opt_3stage, megamoe/large_opt.py:367-508. */
+int mm_fp8_w8a8_mega_moe(void* y, const void* w1, const float* s1, const void* w2, const float* s2, int* stats,
+                         void* sym_base, void* scratch, const uint64_t* peer_ptrs, int rank, int R,
+                         int T_max, int E_loc, int num_tokens, int K, int H, int I, float activation_clamp,
+                         int mode, const int* runtime_num_tokens, void* stream);
+
+/* Copy the 5-word status {code, phase, rank, expected, observed} of the scratch buffer to the host
+ * (synchronises the stream).  code 0 = no bounded wait expired.  The reference aborts the process instead
+ * (deep_gemm/include/deep_gemm/comm/mega_moe_dcu.cuh:85-89). */
+int mm_read_status(const void* scratch, void* stream, int32_t* out5);
+
+/* Set the limits of the device-side bounded waits (milliseconds): cross-rank barriers and in-kernel pipelines. */
+int mm_set_timeouts(int rank_barrier_ms, int pipeline_ms);
+
+/* JSON description of the build.  Replaces get_mega_moe_hip_build_config, csrc/apis/mega_dcu.hpp:28-39. */
+int mm_build_config(char* json, int capacity);
+
+/* Number of kernels the library has launched in this process (all entry points). */
+int64_t mm_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,164 @@
+"""Shared helpers for the parity tests: build a seeded case, run the CPU oracle, run the CUDA path through the
+`megamoe` API (which calls the C ABI), and compare stage by stage."""
+from __future__ import annotations
+
+import os
+import sys
+from dataclasses import dataclass
+from typing import List, Optional
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from oracle import moe_oracle as orc  # noqa: E402
+
+# acceptance bar for layer outputs: max-abs error <= 2e-2 * rms(reference output), cosine similarity >= 0.999
+MAX_ABS_OVER_RMS = 2e-2
+MIN_COSINE = 0.999
+
+
+@dataclass
+class Case:
+    R: int
+    E: int
+    K: int
+    H: int
+    I: int
+    tokens: List[int]
+    x_bf16: List[torch.Tensor]
+    x_q: List[torch.Tensor]
+    x_s: List[torch.Tensor]
+    idx: List[torch.Tensor]
+    w: List[torch.Tensor]
+    w1_bf16: List[torch.Tensor]
+    w2_bf16: List[torch.Tensor]
+    w1_q: List[torch.Tensor]
+    w1_s: List[torch.Tensor]
+    w2_q: List[torch.Tensor]
+    w2_s: List[torch.Tensor]
+
+
+def make_case(R, E, K, H, I, tokens, seed=0, zipf=False, invalid_fraction=0.0) -> Case:
+    """tokens: per-rank token counts.  invalid_fraction > 0 marks some routes invalid (-1 expert or zero weight)."""
+    xb, xq, xs, idx, w = [], [], [], [], []
+    for r in range(R):
+        x = orc.make_inputs(tokens[r], H, seed=seed * 1000 + r)
+        q, s = orc.cast_to_fp8_channelwise(x) if tokens[r] else (torch.empty((0, H), dtype=torch.float8_e4m3fn), torch.empty((0,)))
+        i_, w_ = orc.make_routing(tokens[r], E, K, seed=seed * 1000 + 100 + r, zipf=zipf)
+        if invalid_fraction > 0 and tokens[r]:
+            g = torch.Generator().manual_seed(seed * 1000 + 500 + r)
+            m = torch.rand(i_.shape, generator=g)
+            i_ = torch.where(m < invalid_fraction / 2, torch.full_like(i_, -1), i_)
+            w_ = torch.where((m >= invalid_fraction / 2) & (m < invalid_fraction), torch.zeros_like(w_), w_)
+        xb.append(x); xq.append(q); xs.append(s); idx.append(i_); w.append(w_)
+    w1b, w2b, w1q, w1s, w2q, w2s = [], [], [], [], [], []
+    for r in range(R):
+        a, b = orc.make_weights(E // R, H, I, seed=seed * 1000 + 200 + r)
+        aq, as_ = orc.cast_grouped_weight_to_fp8_channelwise(a)
+        bq, bs_ = orc.cast_grouped_weight_to_fp8_channelwise(b)
+        w1b.append(a); w2b.append(b); w1q.append(aq); w1s.append(as_); w2q.append(bq); w2s.append(bs_)
+    return Case(R, E, K, H, I, list(tokens), xb, xq, xs, idx, w, w1b, w2b, w1q, w1s, w2q, w2s)
+
+
+def run_oracle(case: Case, clamp=None, variant="fused", trace=False):
+    return orc.moe_layer(case.x_q, case.x_s, case.idx, case.w, case.w1_q, case.w1_s, case.w2_q, case.w2_s,
+                         case.E, clamp, variant, trace=trace)
+
+
+def run_cuda_rank(case: Case, rank: int, group=None, clamp=None, t_max: Optional[int] = None, stats=None,
+                  marlin=False, sb=None, keep=False, quantise_on_device=True, **kwargs):
+    """Run one rank of the case on the current CUDA device through the megamoe API. Returns (y, sym_buffer|None)."""
+    import megamoe
+    dev = torch.device("cuda", torch.cuda.current_device())
+    T = case.tokens[rank]
+    t_cap = t_max if t_max is not None else max(max(case.tokens), 1)
+    own = sb is None
+    if own:
+        sb = megamoe.get_symm_buffer_for_mega_moe(group, case.E, t_cap, case.K, case.H, case.I)
+    if quantise_on_device:
+        w1 = megamoe.transform_fp8_weights_for_mega_moe(case.w1_bf16[rank].to(dev), case.w2_bf16[rank].to(dev),
+                                                        layout="marlin" if marlin else "native")
+        l1, l2 = w1
+        if T:
+            xq, xs = megamoe.cast_to_fp8_channelwise(case.x_bf16[rank].to(dev))
+        else:
+            xq = torch.empty((0, case.H), dtype=torch.float8_e4m3fn, device=dev); xs = torch.empty((0,), device=dev)
+    else:
+        l1 = (case.w1_q[rank].to(dev), case.w1_s[rank].to(dev)); l2 = (case.w2_q[rank].to(dev), case.w2_s[rank].to(dev))
+        xq, xs = case.x_q[rank].to(dev), case.x_s[rank].to(dev)
+    sb.x[:T].copy_(xq); sb.x_sf[:T].copy_(xs)
+    sb.topk_idx[:T].copy_(case.idx[rank].to(dev)); sb.topk_weights[:T].copy_(case.w[rank].to(dev))
+    y = torch.full((T, case.H), float("nan"), dtype=torch.bfloat16, device=dev)
+    megamoe.fp8_w8a8_mega_moe(y, l1, l2, sb, cumulative_local_expert_recv_stats=stats, activation_clamp=clamp, **kwargs)
+    sb.check_status()
+    if own and not keep:
+        out = y.cpu()
+        sb.destroy()
+        return out, None
+    return y.cpu(), sb
+
+
+def compare_stages(case: Case, rank: int, sb, lay: orc.RouteLayout, tr: orc.LayerTrace, log=print) -> dict:
+    """Compare every intermediate the CUDA path leaves in its buffers with the oracle's. Returns a dict of findings."""
+    out = {}
+    T, K, H, I = case.tokens[rank], case.K, case.H, case.I
+    E_loc = case.E // case.R
+    # stage 1: quantised inputs
+    out["x_q_equal"] = bool(torch.equal(sb.x[:T].cpu().view(torch.uint8), case.x_q[rank].view(torch.uint8)))
+    out["x_s_equal"] = bool(torch.equal(sb.x_sf[:T].cpu(), case.x_s[rank]))
+    # stage 3: routing
+    dest = sb.scratch_view("dest_row", (sb.num_max_tokens_per_rank, K), torch.int32)[:T].cpu().numpy()
+    out["dest_row_equal"] = bool(np.array_equal(dest, lay.dest_row[rank]))
+    tot = sb.scratch_view("expert_total", (E_loc,), torch.int32).cpu().numpy()
+    off = sb.scratch_view("expert_off", (E_loc,), torch.int32).cpu().numpy()
+    out["totals_equal"] = bool(np.array_equal(tot, lay.totals[rank * E_loc:(rank + 1) * E_loc]))
+    out["pool_off_equal"] = bool(np.array_equal(off, lay.pool_off[rank * E_loc:(rank + 1) * E_loc]))
+    plan = sb.scratch_view("plan", (8,), torch.int32).cpu().numpy()
+    n = lay.pool_rows[rank]
+    out["plan_rows_equal"] = bool(plan[1] == n and plan[0] == n // 128)
+    # dispatch: pool rows + metadata (only rows sent by ranks that ran on this device are meaningful when R == 1)
+    sr, st, ss = lay.row_src_rank[rank], lay.row_src_token[rank], lay.row_src_slot[rank]
+    validrows = np.nonzero(sr >= 0)[0]
+    pool = sb.symm_view("pool_x", (sb.pool_rows, H), torch.uint8)[:n].cpu()
+    meta = sb.symm_view("pool_meta", (sb.pool_rows, 4), torch.int32)[:n].cpu()
+    ok_rows = True; ok_meta = True
+    for r in range(case.R):
+        m = validrows[sr[validrows] == r]
+        if m.size == 0:
+            continue
+        tt = torch.from_numpy(st[m].astype(np.int64))
+        exp = case.x_q[r].view(torch.uint8)[tt]
+        ok_rows &= bool(torch.equal(pool[torch.from_numpy(m)], exp))
+        mm_ = meta[torch.from_numpy(m)]
+        ok_meta &= bool(torch.equal(mm_[:, 0].contiguous().view(torch.float32), case.x_s[r][tt]))
+        ok_meta &= bool(torch.equal(mm_[:, 1].contiguous().view(torch.float32), case.w[r][tt, torch.from_numpy(ss[m].astype(np.int64))]))
+        ok_meta &= bool(torch.equal(mm_[:, 2], tt.to(torch.int32)))
+        ok_meta &= bool(torch.equal(mm_[:, 3], torch.from_numpy(((r << 8) | ss[m]).astype(np.int32))))
+    out["pool_rows_equal"] = ok_rows
+    out["pool_meta_equal"] = ok_meta
+    # GEMM1 + activation
+    vr = torch.from_numpy(validrows)
+    act = sb.scratch_view("act_bf16", (sb.pool_rows, I), torch.bfloat16)[:n].cpu().float()[vr]
+    ref = tr.act[rank][vr]
+    if ref.numel():
+        rms = ref.pow(2).mean().sqrt().item()
+        out["act_max_abs_over_rms"] = (act - ref).abs().max().item() / max(rms, 1e-30)
+        s2 = sb.scratch_view("act_scale", (sb.pool_rows,), torch.float32)[:n].cpu()[vr]
+        out["act_scale_max_rel"] = ((s2 - tr.act_scale[rank][vr]).abs() / tr.act_scale[rank][vr]).max().item()
+        aq = sb.scratch_view("act_fp8", (sb.pool_rows, I), torch.uint8)[:n].cpu()[vr]
+        out["act_q_mismatch_frac"] = (aq != tr.act_q[rank][vr]).float().mean().item()
+    for k, v in out.items():
+        log(f"  [rank {rank}] {k}: {v}")
+    return out
+
+
+def assert_layer_close(y: torch.Tensor, y_ref: torch.Tensor, what=""):
+    assert y.shape == y_ref.shape, (y.shape, y_ref.shape)
+    assert not torch.isnan(y.float()).any(), f"{what}: NaN in output"
+    err, cos = orc.parity_metrics(y, y_ref)
+    assert err <= MAX_ABS_OVER_RMS and cos >= MIN_COSINE, f"{what}: max_abs/rms={err:.4g} cosine={cos:.6f}"
+    return err, cos

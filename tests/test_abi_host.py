@@ -1,0 +1,119 @@
+"""Host-side checks that need no GPU: the library loads, exports every declared symbol, and its layout arithmetic."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "megamoe_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(mm_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol(built_lib):
+    from deepgemm_b200 import _lib
+    declared = _declared_symbols()
+    assert declared, "no declarations found"
+    for name in declared:
+        assert hasattr(built_lib, name), f"{name} declared in include/megamoe_b200.h but not exported"
+    assert sorted(_lib.EXPORTED_SYMBOLS) == declared
+
+
+def test_token_alignment_and_build_config(built_lib):
+    from deepgemm_b200 import _lib
+    assert built_lib.mm_token_alignment() == 384
+    cfg = _lib.build_config()
+    assert cfg["operator"] == "fp8_w8a8_mega_moe" and cfg["arch"] == "sm_100a"
+    assert cfg["weight_scale_mode"] == "channelwise_fp32"
+
+
+def test_symm_layout_regions_are_disjoint_and_sized(built_lib):
+    from deepgemm_b200 import _lib
+    R, E, T, K, H, I = 8, 256, 8448, 6, 4096, 2048
+    off, total = _lib.symm_buffer_layout(R, E, T, K, H, I)
+    sizes = {"peer_ptrs": 8 * 16, "signals": 4 * 4 * 16, "runtime_num_tokens": 4, "count_matrix": 4 * R * E, "x": T * H,
+             "x_sf": 4 * T, "topk_idx": 8 * T * K, "topk_weights": 4 * T * K, "pool_x": off["pool_rows"] * H,
+             "pool_meta": 16 * off["pool_rows"], "combine": 2 * K * T * H}
+    order = sorted(sizes, key=lambda k: off[k])
+    for a, b in zip(order, order[1:]):
+        assert off[a] + sizes[a] <= off[b], (a, b)
+    assert off[order[-1]] + sizes[order[-1]] <= total
+    for k in sizes:
+        assert off[k] % 256 == 0
+    # worst case: every route of every rank lands on this rank, plus per-expert padding to 128 rows
+    assert off["pool_rows"] >= R * T * K + (E // R) * 127 and off["pool_rows"] % 128 == 0
+    # the caller-visible part equals the reference's formula (csrc/apis/mega_dcu.hpp:104-116) up to alignment
+    assert sizes["combine"] == K * T * H * 2
+
+
+def test_scratch_layout_regions(built_lib):
+    from deepgemm_b200 import _lib
+    R, E, T, K, H, I = 2, 8, 384, 2, 512, 256
+    off, total = _lib.scratch_layout(R, E, T, K, H, I)
+    rows = _lib.symm_buffer_layout(R, E, T, K, H, I)[0]["pool_rows"]
+    assert off["act_fp8"] + rows * I <= total
+    assert off["act_bf16"] + rows * I * 2 <= off["act_fp8"]
+    assert off["route_blocks"] == (T * K + 255) // 256
+
+
+@pytest.mark.parametrize("args", [
+    (0, 8, 384, 2, 512, 256), (3, 8, 384, 2, 512, 256), (1, 8, 384, 2, 500, 256), (1, 8, 384, 2, 512, 200),
+    (1, 8, 384, 40, 512, 256), (1, 2048, 384, 2, 512, 256), (17, 34, 384, 2, 512, 256),
+])
+def test_bad_shapes_are_rejected_with_a_message(built_lib, args):
+    from deepgemm_b200 import _lib
+    with pytest.raises(_lib.MegaMoeError):
+        _lib.symm_buffer_layout(*args)
+    assert built_lib.mm_last_error()
+
+
+def test_layer_entry_point_validates_before_touching_the_device(built_lib):
+    """Argument errors are reported without any CUDA call (so this runs on a machine without a GPU)."""
+    peers = (ctypes.c_uint64 * 16)(0x1000)
+    rc = built_lib.mm_fp8_w8a8_mega_moe(0x10, 0x10, 0x10, 0x10, 0x10, None, 0x1000, 0x10, peers, 0, 1, 384, 8, 500, 2, 512, 256,
+                                        float("inf"), 0, None, None)
+    assert rc != 0 and b"too many tokens" in built_lib.mm_last_error()
+    rc = built_lib.mm_fp8_w8a8_mega_moe(0x10, 0x10, 0x10, 0x10, 0x10, None, 0x2000, 0x10, peers, 0, 1, 384, 8, 10, 2, 512, 256,
+                                        float("inf"), 0, None, None)
+    assert rc != 0 and b"peer_ptrs" in built_lib.mm_last_error()
+    rc = built_lib.mm_quant_per_token(0x10, 4, 12, 0x10, 0x10, None)
+    assert rc != 0
+
+
+def test_python_api_surface_and_selector():
+    import megamoe
+    import numpy as np
+    for name in ["SymmBuffer", "cast_to_fp8_channelwise", "cast_grouped_weight_to_fp8_channelwise",
+                 "weight8bit_nt_kpack2_marlin", "get_mega_moe_hip_build_config", "get_symm_buffer_for_mega_moe",
+                 "transform_fp8_weights_for_mega_moe", "deepep_deepgemm_preprocess_channelwise",
+                 "deepep_deepgemm_postprocess_channelwise", "fp8_mega_moe", "fp8_w8a8_mega_moe"]:
+        assert hasattr(megamoe, name)
+    assert megamoe.fp8_w8a8_mega_moe is megamoe.fp8_mega_moe
+    gold = np.load(os.path.join(ROOT, "tests", "golden", "ref_quant.npz"))
+    for mode, n, want in zip(gold["selector_modes"], gold["selector_tokens"], gold["selector_result"]):
+        assert megamoe._large_opt_3stage_selected(int(n), str(mode), 128) == bool(want)
+
+
+def test_marlin_helper_matches_reference_fixture():
+    import megamoe
+    import numpy as np
+    import torch
+    gold = np.load(os.path.join(ROOT, "tests", "golden", "ref_quant.npz"))
+    q = torch.from_numpy(gold["w1_q"].copy()).view(torch.float8_e4m3fn)
+    m = megamoe.weight8bit_nt_kpack2_marlin(q)
+    assert np.array_equal(m.view(torch.uint8).numpy(), gold["w1_marlin"])
+    with pytest.raises(ValueError):
+        megamoe.weight8bit_nt_kpack2_marlin(q, k_tile=8)
+
+
+def test_cpu_tensors_are_refused():
+    import megamoe
+    import torch
+    with pytest.raises(RuntimeError):
+        megamoe.cast_to_fp8_channelwise(torch.zeros((2, 16), dtype=torch.bfloat16))
+    with pytest.raises(ValueError):
+        megamoe.cast_to_fp8_channelwise(torch.zeros((16,), dtype=torch.bfloat16))

@@ -1,0 +1,148 @@
+"""The CPU oracle against the fixtures generated from the reference's own torch helpers (tests/golden/ref_quant.npz,
+made by tests/golden/make_golden.py), and the C restatement against the torch restatement."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import moe_oracle as orc
+
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+
+
+@pytest.fixture(scope="module")
+def ref():
+    return np.load(os.path.join(GOLD, "ref_quant.npz"))
+
+
+def _bf16(bits):
+    return torch.from_numpy(bits.copy()).view(torch.bfloat16)
+
+
+def test_per_token_cast_matches_reference(ref):
+    x = _bf16(ref["x_bf16_bits"])
+    q, s = orc.cast_to_fp8_channelwise(x)
+    assert np.array_equal(q.view(torch.uint8).numpy(), ref["x_q"])
+    assert np.array_equal(s.numpy(), ref["x_scale"])
+    # the zero row takes the 1e-4 floor
+    assert s[5].item() == np.float32(1.0e-4) / np.float32(448.0)
+
+
+def test_c_codec_matches_reference_on_rounding_edges(ref):
+    x = ref["edge_x"]
+    assert ref["edge_scale"][0] == 1.0
+    codes = orc.c_e4m3_encode(x)
+    # -0.0 and +0.0 differ only in the sign bit, which the reference keeps as well
+    assert np.array_equal(codes, ref["edge_q"][0])
+
+
+def test_c_quant_rows_matches_reference(ref):
+    x = _bf16(ref["x_bf16_bits"]).float().numpy()
+    q, s = orc.c_quant_rows(x)
+    assert np.array_equal(s, ref["x_scale"])
+    assert np.array_equal(q, ref["x_q"])
+
+
+def test_c_decode_is_inverse_of_torch_codes():
+    codes = np.arange(256, dtype=np.uint8)
+    ref_vals = torch.from_numpy(codes.copy()).view(torch.float8_e4m3fn).float().numpy()
+    got = orc.c_e4m3_decode(codes)
+    assert np.array_equal(np.isnan(got), np.isnan(ref_vals))
+    m = ~np.isnan(got)
+    assert np.array_equal(got[m], ref_vals[m])
+    # encode(decode(c)) == c for every finite code
+    assert np.array_equal(orc.c_e4m3_encode(got[m]), codes[m])
+
+
+def test_c_encode_dense_sweep_matches_torch():
+    g = torch.Generator().manual_seed(3)
+    x = torch.cat([torch.randn(200000, generator=g) * 100, torch.randn(200000, generator=g), torch.randn(100000, generator=g) * 0.01])
+    x = x.clamp(-448, 448)
+    want = x.to(torch.float8_e4m3fn).view(torch.uint8).numpy()
+    assert np.array_equal(orc.c_e4m3_encode(x.numpy()), want)
+
+
+def test_grouped_weight_cast_and_marlin_match_reference(ref):
+    w1 = _bf16(ref["w1_bf16_bits"]); w2 = _bf16(ref["w2_bf16_bits"])
+    q, s = orc.cast_grouped_weight_to_fp8_channelwise(w1)
+    assert np.array_equal(q.view(torch.uint8).numpy(), ref["w1_q"])
+    assert np.array_equal(s.numpy(), ref["w1_scale"])
+    m = orc.marlin_kpack2(q.view(torch.uint8))
+    assert np.array_equal(m.numpy(), ref["w1_marlin"])
+    assert torch.equal(orc.marlin_kpack2_inverse(m, 64, 128), q.view(torch.uint8))
+    q2, s2 = orc.cast_grouped_weight_to_fp8_channelwise(w2)
+    assert np.array_equal(orc.marlin_kpack2(q.view(torch.uint8)).numpy(), ref["t1"])
+    assert np.array_equal(orc.marlin_kpack2(q2.view(torch.uint8)).numpy(), ref["t2"])
+    assert np.array_equal(s.numpy(), ref["t1s"]) and np.array_equal(s2.numpy(), ref["t2s"])
+
+
+def test_marlin_index_formula():
+    """Element (row, k) lands at the offset given by the reference's marlin_nt_kpack2_offset
+    (deep_gemm/include/deep_gemm/layout/mega_moe_dcu.cuh:50-66)."""
+    rows, k = 32, 48
+    w = torch.arange(rows * k, dtype=torch.int32).reshape(1, rows, k)
+    m = orc.marlin_kpack2(w).reshape(-1)
+    for r, kk in [(0, 0), (1, 0), (0, 1), (15, 15), (16, 0), (17, 33), (31, 47)]:
+        off = ((r // 16) * k + (kk // 16) * 16) * 16 + (r % 16) * 16 + (kk % 16)
+        assert m[off].item() == r * k + kk
+
+
+def test_layer_regression_vectors():
+    """The oracle reproduces its committed outputs for the small configuration (tolerance: fp32 summation order may
+    differ between hosts)."""
+    gold = np.load(os.path.join(GOLD, "layer_small.npz"))
+    import moe_case as mc
+    for tag, R in (("r1", 1), ("r2", 2)):
+        E, K, H, I, T = 8, 2, 512, 256, 256
+        xs, sx, idx, wt, w1q, w1s, w2q, w2s = [], [], [], [], [], [], [], []
+        for r in range(R):
+            xb = orc.make_inputs(T // R, H, seed=0 + r)
+            q_, s_ = orc.cast_to_fp8_channelwise(xb)
+            i_, w_ = orc.make_routing(T // R, E, K, seed=100 + r)
+            a, b = orc.make_weights(E // R, H, I, seed=200 + r)
+            aq, as_ = orc.cast_grouped_weight_to_fp8_channelwise(a)
+            bq, bs_ = orc.cast_grouped_weight_to_fp8_channelwise(b)
+            xs.append(q_); sx.append(s_); idx.append(i_); wt.append(w_)
+            w1q.append(aq); w1s.append(as_); w2q.append(bq); w2s.append(bs_)
+        for variant in ("fused", "staged"):
+            for clamp in (None, 10.0):
+                ys, lay, _ = orc.moe_layer(xs, sx, idx, wt, w1q, w1s, w2q, w2s, E, clamp, variant)
+                key = f"{tag}_{variant}_{'noclamp' if clamp is None else 'clamp10'}_y_bits"
+                want = torch.from_numpy(gold[key].copy()).view(torch.bfloat16)
+                got = torch.stack([y[:16] for y in ys])
+                err, cos = orc.parity_metrics(got, want)
+                assert err < 5e-3 and cos > 0.99999, (key, err, cos)
+        assert np.array_equal(lay.counts, gold[tag + "_counts"])
+        assert np.array_equal(lay.pool_off, gold[tag + "_pool_off"])
+        assert np.array_equal(np.stack(lay.dest_row), gold[tag + "_dest_row"])
+
+
+def test_fused_and_staged_variants_are_close_but_not_interchangeable():
+    """The reference's two kernels round at different points (bf16 before vs after SwiGLU), which flips about one
+    FP8 code in twenty; they agree in cosine but NOT within the 2e-2*rms max-abs bar, so a CUDA path has to be
+    compared with the oracle variant it implements (the persistent-kernel one, "fused")."""
+    import moe_case as mc
+    case = mc.make_case(1, 8, 2, 512, 256, [256])
+    for clamp in (None, 10.0):
+        a, _, _ = mc.run_oracle(case, clamp, "fused")
+        b, _, _ = mc.run_oracle(case, clamp, "staged")
+        err, cos = orc.parity_metrics(a[0], b[0])
+        assert cos >= 0.999 and err < 0.5, (err, cos)
+
+
+def test_quantised_layer_tracks_unquantised_bf16_model():
+    """Self-consistency: the W8A8 layer stays within FP8 error of the same MoE evaluated on the unquantised weights."""
+    import moe_case as mc
+    case = mc.make_case(1, 8, 2, 512, 256, [128])
+    y, _, _ = mc.run_oracle(case)
+    x = case.x_bf16[0].float()
+    ref = torch.zeros((128, 512))
+    for t in range(128):
+        for s in range(2):
+            e = int(case.idx[0][t, s])
+            gu = case.w1_bf16[0][e].float() @ x[t]
+            a = torch.nn.functional.silu(gu[:256]) * gu[256:] * case.w[0][t, s]
+            ref[t] += case.w2_bf16[0][e].float() @ a
+    err, cos = orc.parity_metrics(y[0], ref)
+    assert cos > 0.995 and err < 0.5, (err, cos)

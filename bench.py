@@ -1,0 +1,340 @@
+#!/usr/bin/env python
+"""Benchmark of the W8A8 channelwise Mega MoE layer on B200.
+
+    python bench.py --gpus N --steps K --warmup W              # this implementation (one process per GPU)
+    python bench.py --impl reference --gpus N --steps K --warmup W   # CPU arm: the oracle port on the host cores
+
+Workload: the DSV4-Flash-shaped layer (256 experts, top-6, hidden 4096, intermediate 2048), 4096 tokens per rank,
+logits ~ N(0,1) routing, EP = N (256/N experts per rank); synthetic seeded data, random-init weights quantised per
+output channel.  One step = one pass of the layer over one batch.  One JSON line is printed by rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for p in (ROOT, os.path.join(ROOT, "tests")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+import torch  # noqa: E402
+
+E, K, H, I = 256, 6, 4096, 2048
+METRIC, UNIT = "moe_layer_tokens_per_s", "tokens/s"
+FLOP_PER_ROW = 2 * 3 * H * I                     # 50.33 MFLOP per routed row (GEMM1 33.55 + GEMM2 16.78)
+# DRAM read+write bytes of one GEMM1 launch at the N=1 workload, from the ncu capture summarised in
+# profiles/gemm1_dsv4_ep1.md (a 32-expert case scaled by the experts processed); None until captured
+GEMM1_DRAM_TRAFFIC_BYTES = None
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()          # the exact process started above
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for n, v in zip(names, r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        busy = sorted(sm)[len(sm) // 2:] if sm else []
+        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def init_dist(n_gpus: int):
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        return dist, dist.group.WORLD, rank, world, local
+    if n_gpus > 1:
+        raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run (one process per GPU)")
+    torch.cuda.set_device(0)
+    return None, None, 0, 1, 0
+
+
+def make_rank_data(rank: int, world: int, tokens: int, dev):
+    """Seeded synthetic inputs and weights of one rank, generated on the device (inputs also kept in pinned host memory)."""
+    import megamoe
+    e_loc = E // world
+    g = torch.Generator(device=dev).manual_seed(1000 + rank)
+    l1q = torch.empty((e_loc, 2 * I // 128, H // 128, 128, 128), dtype=torch.float8_e4m3fn, device=dev)   # tiled layout
+    l1s = torch.empty((e_loc, 2 * I), dtype=torch.float32, device=dev)
+    l2q = torch.empty((e_loc, H // 128, I // 128, 128, 128), dtype=torch.float8_e4m3fn, device=dev)
+    l2s = torch.empty((e_loc, H), dtype=torch.float32, device=dev)
+    step = 16
+    for e0 in range(0, e_loc, step):   # a few experts at a time bounds the bf16 temporaries
+        n = min(step, e_loc - e0)
+        w1 = (torch.randn((n, 2 * I, H), generator=g, device=dev, dtype=torch.float32) / H ** 0.5).to(torch.bfloat16)
+        w2 = (torch.randn((n, H, I), generator=g, device=dev, dtype=torch.float32) / I ** 0.5).to(torch.bfloat16)
+        (a, as_), (b, bs_) = megamoe.transform_fp8_weights_for_mega_moe(w1, w2)
+        l1q[e0:e0 + n], l1s[e0:e0 + n], l2q[e0:e0 + n], l2s[e0:e0 + n] = a, as_, b, bs_
+        del w1, w2, a, b
+    x = torch.randn((tokens, H), generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    logits = torch.randn((tokens, E), generator=g, device=dev, dtype=torch.float32)
+    w, idx = torch.topk(torch.softmax(logits, dim=-1), K, dim=-1)
+    w = (w / w.sum(dim=-1, keepdim=True)).float()
+    return (l1q, l1s), (l2q, l2s), x, idx.to(torch.int64), w
+
+
+def _plain(w):
+    """Weights as plain [E, rows, K] on the host (undo the tiled packing if present)."""
+    if w.dim() == 5:
+        g, rt, kt = w.shape[:3]
+        w = w.view(torch.uint8).permute(0, 1, 3, 2, 4).reshape(g, rt * 128, kt * 128).view(torch.float8_e4m3fn)
+    return w.cpu()
+
+
+def cpu_baseline(l1, l2, x_q, x_s, idx, w, n_experts: int, threads: int, repeats: int = 1):
+    """Time the CPU oracle on the rows of the first `n_experts` experts of rank 0 (a bounded sample of the workload).
+    Returns (tokens/s equivalent, rows in the sample, seconds)."""
+    from oracle import moe_oracle as orc
+    torch.set_num_threads(threads)
+    keep = idx < n_experts
+    idx_s = torch.where(keep, idx, torch.full_like(idx, -1)).cpu()
+    args = ([x_q.cpu()], [x_s.cpu()], [idx_s], [w.cpu()],
+            [_plain(l1[0][:n_experts])], [l1[1][:n_experts].cpu()], [_plain(l2[0][:n_experts])], [l2[1][:n_experts].cpu()])
+    rows = int(keep.sum().item())
+    best = float("inf")
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        orc.moe_layer(*args, n_experts, None, "fused")
+        best = min(best, time.perf_counter() - t0)
+    return rows / K / best, rows, best
+
+
+def run_reference_arm(args):
+    """--impl reference: the reference has no runnable CPU or CUDA implementation of this path (HIP/gfx938 only), so
+    this arm times the CPU restatement of its arithmetic (oracle/moe_oracle.py) on the host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import moe_oracle as orc
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    tokens, n_exp = args.tokens, 8
+    g = torch.Generator().manual_seed(1000)
+    w1 = (torch.randn((n_exp, 2 * I, H), generator=g) / H ** 0.5).to(torch.bfloat16)
+    w2 = (torch.randn((n_exp, H, I), generator=g) / I ** 0.5).to(torch.bfloat16)
+    l1 = orc.cast_grouped_weight_to_fp8_channelwise(w1); l2 = orc.cast_grouped_weight_to_fp8_channelwise(w2)
+    x = torch.randn((tokens, H), generator=g).to(torch.bfloat16)
+    xq, xs = orc.cast_to_fp8_channelwise(x)
+    idx, w = orc.make_routing(tokens, E, K, seed=1000)
+    times, rows = [], 0
+    for i in range(args.warmup + args.steps):
+        v, rows, t = cpu_baseline(l1, l2, xq, xs, idx, w, n_exp, threads)
+        if i >= args.warmup:
+            times.append(t)
+    t_step = sum(times) / len(times)
+    value = rows / K / t_step
+    sample = f"rows routed to the first {n_exp} of {E} experts ({rows} of {tokens * K} routed rows) per step"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": t_step * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"DSV4-Flash MoE layer E={E} top{K} H={H} I={I}, {tokens} tokens/rank, CPU sample", "l2": "n/a (CPU)"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--tokens", type=int, default=4096, help="tokens per rank")
+    ap.add_argument("--experts", type=int, default=E, help="total experts (reduce only for small profiler captures)")
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    globals()["E"] = args.experts
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    dist, group, rank, world, local = init_dist(args.gpus)
+    dev = torch.device("cuda", local)
+    import megamoe
+    from deepgemm_b200 import _lib
+    T = args.tokens
+    e_loc = E // world
+    l1, l2, x_bf16, idx, w = make_rank_data(rank, world, T, dev)
+    sb = megamoe.get_symm_buffer_for_mega_moe(group, E, T, K, H, I)
+    y = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
+    stream = torch.cuda.current_stream().cuda_stream
+    lib = _lib.lib()
+
+    def quantise_into_buffer(src):
+        _lib.check(lib.mm_quant_per_token(src.data_ptr(), T, H, sb.x.data_ptr(), sb.x_sf.data_ptr(), stream))
+
+    def layer():
+        megamoe.fp8_w8a8_mega_moe(y, l1, l2, sb)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier(group)
+            torch.cuda.synchronize()
+
+    def max_over_ranks(v: float) -> float:
+        if dist is None:
+            return v
+        t = torch.tensor([v], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- device-resident arm: inputs already quantised in the symmetric buffer ----------------------------------
+    quantise_into_buffer(x_bf16)
+    sb.topk_idx[:T].copy_(idx); sb.topk_weights[:T].copy_(w)
+    for _ in range(max(args.warmup, 3)):
+        layer()
+    barrier()
+    sb.check_status()
+    sampler = ClockSampler(local)
+    sampler.start()
+    launches0 = _lib.launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record()
+    for _ in range(args.steps):
+        layer()
+    ev1.record()
+    barrier()
+    launches = _lib.launch_count() - launches0
+    ms_step = max_over_ranks(ev0.elapsed_time(ev1) / args.steps)
+    sb.check_status()
+
+    # ---- end-to-end arm: host buffers in, host buffer out, every step ------------------------------------------
+    hx = x_bf16.cpu().pin_memory(); hidx = idx.cpu().pin_memory(); hw = w.cpu().pin_memory()
+    hy = torch.empty((T, H), dtype=torch.bfloat16).pin_memory()
+    dx = torch.empty_like(x_bf16)
+
+    def e2e_step():
+        dx.copy_(hx, non_blocking=True)
+        sb.topk_idx[:T].copy_(hidx, non_blocking=True)
+        sb.topk_weights[:T].copy_(hw, non_blocking=True)
+        quantise_into_buffer(dx)
+        layer()
+        hy.copy_(y, non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    ev2, ev3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev2.record()
+    for _ in range(args.steps):
+        e2e_step()
+    ev3.record()
+    barrier()
+    e2e_ms = max_over_ranks(ev2.elapsed_time(ev3) / args.steps)
+    clocks = sampler.stop()
+    h2d = T * H * 2 + T * K * 8 + T * K * 4
+    d2h = T * H * 2
+
+    # ---- per-stage times (CUDA events recorded by the library on the launching stream) --------------------------
+    lib.mm_set_stage_timing(1)
+    acc = {}
+    n_rep = max(3, min(10, args.steps))
+    for _ in range(n_rep):
+        layer()
+        for k_, v in _lib.stage_times().items():
+            acc[k_] = acc.get(k_, 0.0) + v / n_rep
+    lib.mm_set_stage_timing(0)
+    stats = torch.zeros((e_loc,), dtype=torch.int32, device=dev)
+    megamoe.fp8_w8a8_mega_moe(y, l1, l2, sb, cumulative_local_expert_recv_stats=stats)
+    rows_recv = int(stats.sum().item())
+    touched = int((stats > 0).sum().item())
+    gemm1_ms = max_over_ranks(acc["gemm1"])
+    # algorithmic bytes of one GEMM1 launch: FP8 gate+up weights and their scales of the touched experts, the received
+    # FP8 rows with their 16-byte metadata, the bf16 activations written
+    gemm1_bytes = touched * (2 * I * H + 4 * 2 * I) + rows_recv * (H + 16) + rows_recv * I * 2
+    hbm_peak, peak_kind = measured_peaks()
+    achieved = gemm1_bytes / (gemm1_ms * 1e-3) / 1e9
+
+    total_rows = T * K * world
+    value = T * world / (ms_step * 1e-3)
+    out = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3",
+        "data": "synthetic",
+        "config": {"workload": f"DSV4-Flash MoE layer: {E} experts top-{K} hidden {H} intermediate {I}, {T} tokens/rank, EP={world}, "
+                               "uniform N(0,1)-logit routing, W8A8 channelwise", "tokens_per_rank": T, "ep": world,
+                   "l2": "weights streamed per step exceed L2 (no flush needed)", "variant": "staged"},
+        "fp8_tflops": total_rows * FLOP_PER_ROW / (ms_step * 1e-3) / 1e12,
+        "e2e": {"value": T * world / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": e2e_ms},
+        "gpu_launches": launches,
+        "clocks": clocks,
+        "roofline": {"kernel": "grouped_gemm_kernel<0> (GEMM1 + SwiGLU)", "bound": "hbm", "achieved": achieved, "peak": hbm_peak,
+                     "unit": "GB/s", "frac": achieved / hbm_peak, "peak_kind": f"of {peak_kind}", "traffic": GEMM1_DRAM_TRAFFIC_BYTES,
+                     "algorithmic_bytes": gemm1_bytes, "ms": gemm1_ms},
+        "stage_ms": {k_: round(v, 4) for k_, v in acc.items()},
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        threads = os.cpu_count() or 1
+        n_exp = 32
+        v, rows, secs = cpu_baseline(l1, l2, sb.x[:T], sb.x_sf[:T], idx, w, n_exp, threads)
+        out["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": threads, "kind": "port",
+                               "sample": f"rows routed to the first {n_exp} of {E} experts ({rows} of {T * K} routed rows), {secs:.1f} s"}
+    if rank == 0:
+        print(json.dumps(out))
+    sb.destroy()
+    if dist is not None:
+        dist.barrier(group)
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -42,7 +42,11 @@ _SIGNATURES = {
     "mm_set_timeouts": (c_int, [c_int, c_int]),
     "mm_build_config": (c_int, [ctypes.c_char_p, c_int]),
     "mm_launch_count": (c_int64, []),
+    "mm_set_stage_timing": (c_int, [c_int]),
+    "mm_get_stage_times": (c_int, [POINTER(c_float), c_int]),
 }
+STAGE_NAMES = ["route_count", "route_exchange", "route_plan", "dispatch", "barrier_dispatch", "gemm1", "requant", "gemm2",
+               "barrier_combine", "reduce"]
 EXPORTED_SYMBOLS = tuple(_SIGNATURES)
 
 _lib = None
@@ -94,6 +98,13 @@ def build_config() -> dict:
     buf = ctypes.create_string_buffer(1024)
     check(lib().mm_build_config(buf, 1024))
     return json.loads(buf.value.decode())
+
+
+def stage_times() -> dict:
+    """Durations (ms) of the stages of the last layer call made with stage timing on."""
+    buf = (c_float * len(STAGE_NAMES))()
+    check(lib().mm_get_stage_times(buf, len(STAGE_NAMES)))
+    return {n: float(v) for n, v in zip(STAGE_NAMES, buf) if v >= 0}
 
 
 def launch_count() -> int:

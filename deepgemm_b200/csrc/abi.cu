@@ -139,6 +139,33 @@ int ensure_gemm_attrs() {
         MM_CUDA(cudaGetLastError());  \
     } while (0)
 
+// Optional per-stage timing of the staged layer call: CUDA events recorded on the caller's stream around every launch.
+std::atomic<int> g_stage_timing{0};
+std::mutex g_stage_mu;
+cudaEvent_t g_stage_ev[MM_NUM_STAGES + 1];
+bool g_stage_ev_made = false;
+bool g_stage_recorded[MM_NUM_STAGES];
+
+int stage_begin(cudaStream_t stream) {
+    if (!g_stage_timing.load()) return 0;
+    std::lock_guard<std::mutex> lk(g_stage_mu);
+    if (!g_stage_ev_made) {
+        for (auto& e : g_stage_ev) MM_CUDA(cudaEventCreate(&e));
+        g_stage_ev_made = true;
+    }
+    for (auto& r : g_stage_recorded) r = false;
+    MM_CUDA(cudaEventRecord(g_stage_ev[0], stream));
+    return 0;
+}
+// called after the launch of stage `id`; stages are launched in increasing id order
+int stage_end(int id, cudaStream_t stream) {
+    if (!g_stage_timing.load()) return 0;
+    std::lock_guard<std::mutex> lk(g_stage_mu);
+    MM_CUDA(cudaEventRecord(g_stage_ev[id + 1], stream));
+    g_stage_recorded[id] = true;
+    return 0;
+}
+
 }  // namespace
 
 extern "C" {
@@ -255,7 +282,8 @@ int mm_fp8_w8a8_mega_moe(void* y, const void* w1, const float* s1, const void* w
     MM_REQUIRE(E_loc > 0, "num_experts_per_rank must be positive");
     const int E = E_loc * R;
     if (int rc = check_shape(R, E, T_max, K, H, I)) return rc;
-    MM_REQUIRE(y && w1 && s1 && w2 && s2 && sym_base && scratch && peer_ptrs, "mm_fp8_w8a8_mega_moe: null pointer");
+    MM_REQUIRE((y || num_tokens == 0) && w1 && s1 && w2 && s2 && sym_base && scratch && peer_ptrs,
+               "mm_fp8_w8a8_mega_moe: null pointer");
     MM_REQUIRE(rank >= 0 && rank < R, "rank out of range");
     MM_REQUIRE(num_tokens >= 0 && num_tokens <= T_max, "too many tokens");
     MM_REQUIRE(peer_ptrs[rank] == reinterpret_cast<uint64_t>(sym_base), "peer_ptrs[rank] must be the local buffer");
@@ -288,9 +316,9 @@ int mm_fp8_w8a8_mega_moe(void* y, const void* w1, const float* s1, const void* w
     uint8_t* sc = rp.scratch;
     CUtensorMap tm_pool, tm_w1, tm_act, tm_w2;
     if (int rc = tensor_map_2d(rp.sym + rp.sl.pool_x, (uint64_t)H, (uint64_t)rp.sl.pool_rows, &tm_pool)) return rc;
-    if (int rc = tensor_map_2d(w1, (uint64_t)H, (uint64_t)E_loc * 2 * I, &tm_w1)) return rc;
+    if (int rc = tensor_map_2d(w1, 128, (uint64_t)E_loc * 2 * I * (H / 128), &tm_w1)) return rc;
     if (int rc = tensor_map_2d(sc + rp.cl.act_fp8, (uint64_t)I, (uint64_t)rp.sl.pool_rows, &tm_act)) return rc;
-    if (int rc = tensor_map_2d(w2, (uint64_t)I, (uint64_t)E_loc * H, &tm_w2)) return rc;
+    if (int rc = tensor_map_2d(w2, 128, (uint64_t)E_loc * H * (I / 128), &tm_w2)) return rc;
 
     mm::GemmParams g1;
     memset(&g1, 0, sizeof(g1));
@@ -313,32 +341,35 @@ int mm_fp8_w8a8_mega_moe(void* y, const void* w1, const float* s1, const void* w
 
     if (mode == MM_MODE_FUSED) return fail(2, "the fused variant is not available in this build");
 
+    if (int rc = stage_begin(stream)) return rc;
+#define MM_STAGE(id) do { MM_LAUNCHED(); if (int rc_ = stage_end(id, stream)) return rc_; } while (0)
     mm::route_count_kernel<<<route_blocks, MM_ROUTE_CHUNK, 0, stream>>>(rp);
-    MM_LAUNCHED();
+    MM_STAGE(MM_STAGE_ROUTE_COUNT);
     mm::route_exchange_kernel<<<1, 1024, 0, stream>>>(rp);
-    MM_LAUNCHED();
+    MM_STAGE(MM_STAGE_ROUTE_EXCHANGE);
     mm::route_plan_kernel<<<1, 1024, 0, stream>>>(rp);
-    MM_LAUNCHED();
+    MM_STAGE(MM_STAGE_ROUTE_PLAN);
     mm::dispatch_kernel<<<route_blocks, MM_ROUTE_CHUNK, 0, stream>>>(rp);
-    MM_LAUNCHED();
+    MM_STAGE(MM_STAGE_DISPATCH);
     if (R > 1) {
         mm::rank_barrier_kernel<<<1, 32, 0, stream>>>(rp, MM_BAR_DISPATCH);
-        MM_LAUNCHED();
+        MM_STAGE(MM_STAGE_BARRIER_DISPATCH);
     }
     mm::grouped_gemm_kernel<0><<<sms, mm::kGemmThreads, mm::kGemmSmemBytes, stream>>>(tm_pool, tm_w1, g1);
-    MM_LAUNCHED();
+    MM_STAGE(MM_STAGE_GEMM1);
     mm::requant_kernel<<<sms * 8, 256, 0, stream>>>(g1.act_bf16, I, g1.plan, g1.mblock_valid, g1.row_amax,
                                                    reinterpret_cast<float*>(sc + rp.cl.act_scale), sc + rp.cl.act_fp8);
-    MM_LAUNCHED();
+    MM_STAGE(MM_STAGE_REQUANT);
     mm::grouped_gemm_kernel<1><<<sms, mm::kGemmThreads, mm::kGemmSmemBytes, stream>>>(tm_act, tm_w2, g2);
-    MM_LAUNCHED();
+    MM_STAGE(MM_STAGE_GEMM2);
     if (R > 1) {
         mm::rank_barrier_kernel<<<1, 32, 0, stream>>>(rp, MM_BAR_COMBINE);
-        MM_LAUNCHED();
+        MM_STAGE(MM_STAGE_BARRIER_COMBINE);
     }
     mm::combine_reduce_kernel<<<sms * 8, 256, 0, stream>>>(rp.sym, rp.sl, E, T_max, K, H, num_tokens, runtime_num_tokens,
                                                           static_cast<__nv_bfloat16*>(y));
-    MM_LAUNCHED();
+    MM_STAGE(MM_STAGE_REDUCE);
+#undef MM_STAGE
     return 0;
 }
 
@@ -372,5 +403,27 @@ int mm_build_config(char* json, int capacity) {
 }
 
 int64_t mm_launch_count(void) { return g_launches.load(); }
+
+int mm_set_stage_timing(int enable) {
+    g_stage_timing.store(enable ? 1 : 0);
+    return 0;
+}
+
+int mm_get_stage_times(float* ms, int n) {
+    MM_REQUIRE(ms && n >= MM_NUM_STAGES, "mm_get_stage_times: need room for %d floats", MM_NUM_STAGES);
+    std::lock_guard<std::mutex> lk(g_stage_mu);
+    MM_REQUIRE(g_stage_ev_made, "no timed call has been made");
+    int last = 0;
+    for (int i = 0; i < MM_NUM_STAGES; ++i) if (g_stage_recorded[i]) last = i + 1;
+    MM_CUDA(cudaEventSynchronize(g_stage_ev[last]));
+    int prev = 0;
+    for (int i = 0; i < MM_NUM_STAGES; ++i) {
+        ms[i] = -1.0f;
+        if (!g_stage_recorded[i]) continue;
+        MM_CUDA(cudaEventElapsedTime(&ms[i], g_stage_ev[prev], g_stage_ev[i + 1]));
+        prev = i + 1;
+    }
+    return 0;
+}
 
 }  // extern "C"

@@ -77,12 +77,24 @@ __global__ void __launch_bounds__(256) requant_kernel(const __nv_bfloat16* __res
         if (lane == 0) act_scale[r] = s;
         const uint4* src = reinterpret_cast<const uint4*>(act + r * inter);
         uint2* dst = reinterpret_cast<uint2*>(act_q + r * inter);
-        for (int v = lane; v < vecs; v += 32) {
-            const uint4 d = src[v];
-            uint2 o;
-            o.x = pack4_e4m3(bf16_lo(d.x) * inv, bf16_hi(d.x) * inv, bf16_lo(d.y) * inv, bf16_hi(d.y) * inv);
-            o.y = pack4_e4m3(bf16_lo(d.z) * inv, bf16_hi(d.z) * inv, bf16_lo(d.w) * inv, bf16_hi(d.w) * inv);
-            dst[v] = o;
+        for (int v0 = 0; v0 < vecs; v0 += 32 * 8) {     // eight independent 16-byte loads in flight per lane
+            uint4 buf[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int v = v0 + i * 32 + lane;
+                if (v < vecs) buf[i] = src[v];
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int v = v0 + i * 32 + lane;
+                if (v < vecs) {
+                    const uint4 d = buf[i];
+                    uint2 o;
+                    o.x = pack4_e4m3(bf16_lo(d.x) * inv, bf16_hi(d.x) * inv, bf16_lo(d.y) * inv, bf16_hi(d.y) * inv);
+                    o.y = pack4_e4m3(bf16_lo(d.z) * inv, bf16_hi(d.z) * inv, bf16_lo(d.w) * inv, bf16_hi(d.w) * inv);
+                    dst[v] = o;
+                }
+            }
         }
     }
 }
@@ -104,13 +116,27 @@ __global__ void __launch_bounds__(256) combine_reduce_kernel(const uint8_t* __re
          i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
         const int t = static_cast<int>(i / vecs), v = static_cast<int>(i - static_cast<int64_t>(t) * vecs);
         float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        for (int s = 0; s < K; ++s) {
-            const int64_t e = topk_idx[static_cast<int64_t>(t) * K + s];
-            const float w = topk_w[static_cast<int64_t>(t) * K + s];
-            if (!(e >= 0 && e < E && w != 0.0f)) continue;
-            const uint4 d = comb[(static_cast<int64_t>(s) * T + t) * vecs + v];
-            acc[0] += bf16_lo(d.x); acc[1] += bf16_hi(d.x); acc[2] += bf16_lo(d.y); acc[3] += bf16_hi(d.y);
-            acc[4] += bf16_lo(d.z); acc[5] += bf16_hi(d.z); acc[6] += bf16_lo(d.w); acc[7] += bf16_hi(d.w);
+        for (int s0 = 0; s0 < K; s0 += 8) {             // up to eight slots' loads in flight, summed in slot order
+            uint4 buf[8];
+            bool ok[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int s = s0 + j;
+                ok[j] = false;
+                if (s < K) {
+                    const int64_t e = topk_idx[static_cast<int64_t>(t) * K + s];
+                    const float w = topk_w[static_cast<int64_t>(t) * K + s];
+                    ok[j] = e >= 0 && e < E && w != 0.0f;
+                    if (ok[j]) buf[j] = comb[(static_cast<int64_t>(s) * T + t) * vecs + v];
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if (!ok[j]) continue;
+                const uint4 d = buf[j];
+                acc[0] += bf16_lo(d.x); acc[1] += bf16_hi(d.x); acc[2] += bf16_lo(d.y); acc[3] += bf16_hi(d.y);
+                acc[4] += bf16_lo(d.z); acc[5] += bf16_hi(d.z); acc[6] += bf16_lo(d.w); acc[7] += bf16_hi(d.w);
+            }
         }
         uint4 o;
         __nv_bfloat162 b;

@@ -66,17 +66,44 @@ __global__ void __launch_bounds__(MM_ROUTE_CHUNK) route_count_kernel(RouteParams
 __global__ void __launch_bounds__(1024) route_exchange_kernel(RouteParams p) {
     const int route_blocks = static_cast<int>(p.cl.route_blocks);
     int* bc = reinterpret_cast<int*>(p.scratch + p.cl.block_counts);
-    for (int e = threadIdx.x; e < p.E; e += blockDim.x) {
-        int run = 0;
-        for (int b = 0; b < route_blocks; ++b) {
-            const int c = bc[static_cast<int64_t>(b) * p.E + e];
-            bc[static_cast<int64_t>(b) * p.E + e] = run;     // exclusive prefix: rows of earlier blocks
-            run += c;
+    // blockDim / E threads share one expert: each sums a contiguous range of blocks, then turns its range into an
+    // exclusive prefix starting from the ranges before it (loads are independent, so they overlap)
+    __shared__ int part_sum[1024];
+    const int parts = max(1, min(static_cast<int>(blockDim.x) / p.E, 32));
+    const int per = (route_blocks + parts - 1) / parts;
+    for (int e0 = 0; e0 < p.E; e0 += blockDim.x / parts) {
+        const int e = e0 + threadIdx.x % (blockDim.x / parts);
+        const int part = threadIdx.x / (blockDim.x / parts);
+        const bool on = e < p.E && part < parts;
+        const int b0 = part * per, b1 = min(route_blocks, b0 + per);
+        int sum = 0;
+        if (on) {
+#pragma unroll 8
+            for (int b = b0; b < b1; ++b) sum += bc[static_cast<int64_t>(b) * p.E + e];
         }
-        for (int r = 0; r < p.R; ++r) {
-            int* cm = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(p.peers[r]) + p.sl.count_matrix);
-            cm[static_cast<int64_t>(p.rank) * p.E + e] = run;
+        part_sum[threadIdx.x] = sum;
+        __syncthreads();
+        if (on) {
+            int run = 0;
+            for (int q = 0; q < part; ++q) run += part_sum[q * (blockDim.x / parts) + threadIdx.x % (blockDim.x / parts)];
+            int vals[8];
+            for (int b = b0; b < b1; b += 8) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) vals[i] = (b + i < b1) ? bc[static_cast<int64_t>(b + i) * p.E + e] : 0;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    if (b + i < b1) bc[static_cast<int64_t>(b + i) * p.E + e] = run;   // rows of earlier blocks
+                    run += vals[i];
+                }
+            }
+            if (part == parts - 1) {
+                for (int r = 0; r < p.R; ++r) {
+                    int* cm = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(p.peers[r]) + p.sl.count_matrix);
+                    cm[static_cast<int64_t>(p.rank) * p.E + e] = run;
+                }
+            }
         }
+        __syncthreads();
     }
     if (p.R > 1) {
         __threadfence_system();
@@ -210,7 +237,20 @@ __global__ void __launch_bounds__(MM_ROUTE_CHUNK) dispatch_kernel(RouteParams p)
         uint8_t* peer = reinterpret_cast<uint8_t*>(p.peers[r_e / p.E_loc]);
         const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<int64_t>(token) * p.H);
         uint4* dst = reinterpret_cast<uint4*>(peer + p.sl.pool_x + static_cast<int64_t>(r_row) * p.H);
-        for (int v = lane; v < p.H / 16; v += 32) dst[v] = src[v];
+        const int nvec = p.H / 16;
+        for (int v0 = 0; v0 < nvec; v0 += 32 * 8) {     // up to eight independent 16-byte loads in flight per lane
+            uint4 buf[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int v = v0 + i * 32 + lane;
+                if (v < nvec) buf[i] = __ldg(src + v);
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int v = v0 + i * 32 + lane;
+                if (v < nvec) dst[v] = buf[i];
+            }
+        }
         if (lane == 0) {
             MmPoolMeta m;
             m.x_scale = x_sf[token];

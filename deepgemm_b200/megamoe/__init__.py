@@ -7,8 +7,9 @@ pointers.  There is no CPU or PyTorch fallback: CUDA tensors are required and a 
 Differences a caller can observe (all supersets of the reference behaviour):
   * any EP size in 1..16 and any shape with hidden % 128 == 0, intermediate % 128 == 0, top-k <= 32 is accepted
     (the reference accepts only EP8 / 256 experts / top-6 / 4096 / 2048: csrc/kernels/mega_moe_fused_hip.cu:94-119);
-  * `transform_fp8_weights_for_mega_moe` returns weights in plain `[E_loc, rows, K]` layout (what TMA wants);
-    weights in the reference's Marlin layout `[E_loc, rows/16, K*16]` are also accepted and un-permuted once;
+  * `transform_fp8_weights_for_mega_moe` returns weights packed in 128x128-byte tiles (one TMA box = 16 contiguous KiB);
+    plain `[E_loc, rows, K]` weights and the reference's Marlin layout `[E_loc, rows/16, K*16]` are also accepted and
+    re-packed once;
   * `group=None` builds a single-rank buffer without torch.distributed;
   * device-side waits are bounded: `SymmBuffer.check_status()` reports a timeout instead of aborting the process.
 """
@@ -134,15 +135,41 @@ def _marlin_inverse(weight: torch.Tensor, rows: int, k: int) -> torch.Tensor:
             .contiguous().reshape(g, rows, k).view(weight.dtype))
 
 
-def transform_fp8_weights_for_mega_moe(l1_weights: torch.Tensor, l2_weights: torch.Tensor, layout: str = "native"):
+def pack_weights_tiled(weight: torch.Tensor) -> torch.Tensor:
+    """[E, rows, K] -> [E, rows/128, K/128, 128, 128]: every 128-row x 128-byte tile contiguous (16 KiB), the K tiles of
+    one row tile adjacent.  This is the layout the GEMM kernels stream from HBM (one TMA box = one contiguous tile); it
+    plays the role the 16x16 Marlin packing plays for the reference's MMAC kernels (megamoe/__init__.py:81-98)."""
+    if weight.dim() != 3:
+        raise ValueError("expected a grouped [E, rows, K] weight tensor")
+    g, rows, k = weight.shape
+    if rows % 128 != 0 or k % 128 != 0:
+        raise ValueError("rows and K must be multiples of 128")
+    out = torch.empty((g, rows // 128, k // 128, 128, 128), dtype=weight.dtype, device=weight.device)
+    src = weight.view(torch.uint8)
+    dst = out.view(torch.uint8)
+    for e in range(g):   # one expert at a time bounds the temporary
+        dst[e].copy_(src[e].reshape(rows // 128, 128, k // 128, 128).permute(0, 2, 1, 3))
+    return out
+
+
+def unpack_weights_tiled(weight: torch.Tensor) -> torch.Tensor:
+    """Inverse of pack_weights_tiled: [E, rows/128, K/128, 128, 128] -> [E, rows, K]."""
+    g, rt, kt = weight.shape[:3]
+    return (weight.view(torch.uint8).permute(0, 1, 3, 2, 4).contiguous().reshape(g, rt * 128, kt * 128).view(weight.dtype))
+
+
+def transform_fp8_weights_for_mega_moe(l1_weights: torch.Tensor, l2_weights: torch.Tensor, layout: str = "tiled"):
     """bf16 [E_loc,2I,H], [E_loc,H,I] -> ((w1_fp8, s1[E_loc,2I]), (w2_fp8, s2[E_loc,H])) (megamoe/__init__.py:280-289).
-    layout="native" keeps [E_loc, rows, K]; layout="marlin" applies the reference's permutation."""
+    layout="tiled" (default) packs for the B200 kernels (see pack_weights_tiled); "native" keeps [E_loc, rows, K];
+    "marlin" applies the reference's permutation.  fp8_mega_moe accepts all three."""
     l1_fp8, l1_scale = cast_grouped_weight_to_fp8_channelwise(l1_weights)
     l2_fp8, l2_scale = cast_grouped_weight_to_fp8_channelwise(l2_weights)
     if layout == "marlin":
         return (weight8bit_nt_kpack2_marlin(l1_fp8), l1_scale), (weight8bit_nt_kpack2_marlin(l2_fp8), l2_scale)
+    if layout == "tiled":
+        return (pack_weights_tiled(l1_fp8), l1_scale), (pack_weights_tiled(l2_fp8), l2_scale)
     if layout != "native":
-        raise ValueError("layout must be 'native' or 'marlin'")
+        raise ValueError("layout must be 'tiled', 'native' or 'marlin'")
     return (l1_fp8, l1_scale), (l2_fp8, l2_scale)
 
 
@@ -172,6 +199,19 @@ class _DeviceMemory:
 def _view(buffer: torch.Tensor, offset: int, shape, dtype: torch.dtype) -> torch.Tensor:
     n = int(math.prod(shape)) * torch.empty((), dtype=dtype).element_size()
     return buffer[offset:offset + n].view(dtype).view(*shape)
+
+
+def _gather_handles(group, payload: bytes):
+    """All-gather one opaque handle per rank; entry r of the result is rank r's handle (megamoe/__init__.py:178-181)."""
+    import torch.distributed as dist
+    gathered = [None] * group.size()
+    dist.all_gather_object(gathered, (group.rank(), payload), group)
+    out = [None] * group.size()
+    for r, raw in gathered:
+        out[r] = raw
+    if any(h is None for h in out):
+        raise RuntimeError("handle exchange is incomplete: a rank did not contribute")
+    return out
 
 
 class SymmBuffer:
@@ -224,10 +264,8 @@ class SymmBuffer:
             buffer_ptr = int(ptr.value)
             self._owned_ptr = buffer_ptr
             self.buffer = torch.as_tensor(_DeviceMemory(buffer_ptr, num_bytes), device=self.device)
-            handles = [None] * self.num_ranks
-            dist.all_gather_object(handles, (self.rank, bytes(handle.raw)), group)
             buffer_ptrs = [0] * self.num_ranks
-            for r, raw in handles:
+            for r, raw in enumerate(_gather_handles(group, bytes(handle.raw))):
                 if r == self.rank:
                     buffer_ptrs[r] = buffer_ptr
                 else:
@@ -328,26 +366,29 @@ def get_symm_buffer_for_mega_moe(group, num_experts: int, num_max_tokens_per_ran
 
 
 # ------------------------------------------------------------------------------------------------ the layer
-_native_weight_cache = {}
+_packed_weight_cache = {}
 
 
-def _native_weight(w: torch.Tensor, rows: int, k: int, what: str) -> torch.Tensor:
-    """Accept [E_loc, rows, K] or the reference's Marlin shape [E_loc, rows/16, K*16] (un-permuted once, cached)."""
-    if w.dim() != 3:
-        raise RuntimeError("weights must be grouped 3D tensors")
-    if w.shape[1] == rows and w.shape[2] == k:
+def _tiled_weight(w: torch.Tensor, rows: int, k: int, what: str) -> torch.Tensor:
+    """Accept the tiled layout [E_loc, rows/128, K/128, 128, 128] as is; plain [E_loc, rows, K] and the reference's
+    Marlin shape [E_loc, rows/16, K*16] are re-packed once and cached (keyed by storage address and version)."""
+    if w.dim() == 5 and tuple(w.shape[1:]) == (rows // 128, k // 128, 128, 128):
         return w if w.is_contiguous() else w.contiguous()
-    if w.shape[1] == rows // 16 and w.shape[2] == k * 16:
-        key = (w.data_ptr(), tuple(w.shape), w._version)
-        hit = _native_weight_cache.get(key)
-        if hit is None:
-            if len(_native_weight_cache) > 16:
-                _native_weight_cache.clear()
-            hit = _marlin_inverse(w, rows, k)
-            _native_weight_cache[key] = hit
-        return hit
-    raise RuntimeError(f"invalid {what} weight shape {tuple(w.shape)}, expected [expert, {rows}, {k}] "
-                       f"or Marlin [expert, {rows // 16}, {k * 16}]")
+    if w.dim() != 3:
+        raise RuntimeError("weights must be grouped 3D tensors (or tiled 5D tensors)")
+    native = w.shape[1] == rows and w.shape[2] == k
+    marlin = w.shape[1] == rows // 16 and w.shape[2] == k * 16
+    if not (native or marlin):
+        raise RuntimeError(f"invalid {what} weight shape {tuple(w.shape)}, expected [expert, {rows}, {k}], "
+                           f"Marlin [expert, {rows // 16}, {k * 16}] or tiled [expert, {rows // 128}, {k // 128}, 128, 128]")
+    key = (w.data_ptr(), tuple(w.shape), w._version)
+    hit = _packed_weight_cache.get(key)
+    if hit is None:
+        if len(_packed_weight_cache) > 16:
+            _packed_weight_cache.clear()
+        hit = pack_weights_tiled(w.contiguous() if native else _marlin_inverse(w, rows, k))
+        _packed_weight_cache[key] = hit
+    return hit
 
 
 def fp8_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer: SymmBuffer,
@@ -405,6 +446,8 @@ def fp8_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer: SymmBuffer
         raise RuntimeError("DCU MegaMoE expects FP8 E4M3 L1/L2 weights")
     if l1_sf.dtype != torch.float32 or l2_sf.dtype != torch.float32:
         raise RuntimeError("DCU MegaMoE expects FP32 channelwise weight scales")
+    if l1_w.dim() not in (3, 5) or l2_w.dim() not in (3, 5):
+        raise RuntimeError("weights must be grouped 3D tensors (or tiled 5D tensors)")
     if l1_sf.dim() != 2 or l2_sf.dim() != 2:
         raise RuntimeError("weight scales must be [expert,row]")
     num_tokens, hidden = int(call_y.size(0)), int(call_y.size(1))
@@ -422,8 +465,8 @@ def fp8_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer: SymmBuffer
         raise RuntimeError("invalid L2 scale shape")
     if num_tokens > sb.num_max_tokens_per_rank:
         raise RuntimeError("too many tokens")
-    w1 = _native_weight(l1_w, 2 * inter, hidden, "L1")
-    w2 = _native_weight(l2_w, hidden, inter, "L2")
+    w1 = _tiled_weight(l1_w, 2 * inter, hidden, "L1")
+    w2 = _tiled_weight(l2_w, hidden, inter, "L2")
     stats_ptr = None
     if cumulative_local_expert_recv_stats is not None:
         st = cumulative_local_expert_recv_stats
@@ -461,6 +504,8 @@ __all__ = [
     "get_mega_moe_hip_build_config",
     "get_symm_buffer_for_mega_moe",
     "transform_fp8_weights_for_mega_moe",
+    "pack_weights_tiled",
+    "unpack_weights_tiled",
     "deepep_deepgemm_preprocess_channelwise",
     "deepep_deepgemm_postprocess_channelwise",
     "fp8_mega_moe",

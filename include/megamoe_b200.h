@@ -31,6 +31,11 @@ enum {
     MM_SCR_EXPERT_OFF, MM_SCR_MBLOCK_EXPERT, MM_SCR_MBLOCK_VALID, MM_SCR_DEST_ROW, MM_SCR_ROW_AMAX,
     MM_SCR_ACT_SCALE, MM_SCR_ACT_BF16, MM_SCR_ACT_FP8, MM_SCR_ROUTE_BLOCKS, MM_SCR_NUM_OFFSETS
 };
+/* stages of one staged layer call, in launch order (indices of mm_get_stage_times) */
+enum {
+    MM_STAGE_ROUTE_COUNT = 0, MM_STAGE_ROUTE_EXCHANGE, MM_STAGE_ROUTE_PLAN, MM_STAGE_DISPATCH, MM_STAGE_BARRIER_DISPATCH,
+    MM_STAGE_GEMM1, MM_STAGE_REQUANT, MM_STAGE_GEMM2, MM_STAGE_BARRIER_COMBINE, MM_STAGE_REDUCE, MM_NUM_STAGES
+};
 /* execution variants of mm_fp8_w8a8_mega_moe */
 enum { MM_MODE_STAGED = 0, MM_MODE_FUSED = 1 };
 
@@ -70,8 +75,11 @@ int mm_init_buffers(void* sym_base, void* scratch, const uint64_t* peer_ptrs, in
 int mm_quant_per_token(const void* x_bf16, int64_t rows, int k, void* out_fp8, float* out_scale, void* stream);
 
 /* The layer.  Inputs x / x_sf / topk_idx / topk_weights are read from the symmetric buffer views; y receives
- * bf16 [num_tokens, H].  w1 fp8 [E_loc, 2I, H] with s1 f32 [E_loc, 2I] (rows [0,I) gate, [I,2I) up); w2 fp8
- * [E_loc, H, I] with s2 f32 [E_loc, H].  stats (nullable) int32 [E_loc] accumulates rows received per local
+ * bf16 [num_tokens, H].  w1 = fp8 weights [E_loc, 2I, H] (rows [0,I) gate, [I,2I) up) with s1 f32 [E_loc, 2I]; w2 = fp8
+ * weights [E_loc, H, I] with s2 f32 [E_loc, H].  Both weight tensors are stored TILED: [E_loc][rows/128][K/128][128][128],
+ * i.e. element (row, k) of expert e at ((e*rows/128 + row/128)*K/128 + k/128)*16384 + (row%128)*128 + k%128, so that every
+ * 128-row x 128-byte TMA box is one contiguous 16 KiB block (the reference packs 16x16 Marlin tiles for its MMAC units
+ * instead, deep_gemm/include/deep_gemm/layout/mega_moe_dcu.cuh:50-66).  stats (nullable) int32 [E_loc] accumulates rows received per local
  * expert.  peer_ptrs: HOST array of the R ranks' symmetric-buffer device addresses (entry `rank` is sym_base).
  * runtime_num_tokens (nullable): device int32 overriding num_tokens (CUDA-graph bucket mode).
  * activation_clamp: +inf for none.  mode: MM_MODE_STAGED or MM_MODE_FUSED.
@@ -95,6 +103,13 @@ int mm_build_config(char* json, int capacity);
 
 /* Number of kernels the library has launched in this process (all entry points). */
 int64_t mm_launch_count(void);
+
+/* Per-stage device timing of the layer call (the reference's test prints per-kernel times with a profiler,
+ * tests/test_mega_moe_dcu.py:794-834; here CUDA events are recorded on the caller's stream around every launch).
+ * mm_set_stage_timing(1) turns recording on for later calls; mm_get_stage_times waits for the last timed call and
+ * fills ms[MM_NUM_STAGES] with each stage's duration in milliseconds (-1 for a stage that did not run). */
+int mm_set_stage_timing(int enable);
+int mm_get_stage_times(float* ms, int n);
 
 #ifdef __cplusplus
 }

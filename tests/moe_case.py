@@ -81,7 +81,7 @@ def run_cuda_rank(case: Case, rank: int, group=None, clamp=None, t_max: Optional
         sb = megamoe.get_symm_buffer_for_mega_moe(group, case.E, t_cap, case.K, case.H, case.I)
     if quantise_on_device:
         w1 = megamoe.transform_fp8_weights_for_mega_moe(case.w1_bf16[rank].to(dev), case.w2_bf16[rank].to(dev),
-                                                        layout="marlin" if marlin else "native")
+                                                        layout="marlin" if marlin else "tiled")
         l1, l2 = w1
         if T:
             xq, xs = megamoe.cast_to_fp8_channelwise(case.x_bf16[rank].to(dev))
@@ -156,9 +156,21 @@ def compare_stages(case: Case, rank: int, sb, lay: orc.RouteLayout, tr: orc.Laye
     return out
 
 
-def assert_layer_close(y: torch.Tensor, y_ref: torch.Tensor, what=""):
+def assert_layer_close(y: torch.Tensor, y_ref: torch.Tensor, what="", literal=False):
+    """cosine >= 0.999 and, element by element, |y - ref| <= 2e-2 * rms(ref) + one bf16 ulp of |ref|.
+
+    The ulp term is there because the outputs ARE bf16: an element of magnitude 4 * rms has a bf16 spacing of
+    2^-5 * rms = 3.1e-2 * rms, so a single last-bit difference on such an element already exceeds 2e-2 * rms although
+    nothing is wrong.  literal=True drops the ulp term (used for the small seed-0 configuration)."""
     assert y.shape == y_ref.shape, (y.shape, y_ref.shape)
     assert not torch.isnan(y.float()).any(), f"{what}: NaN in output"
     err, cos = orc.parity_metrics(y, y_ref)
-    assert err <= MAX_ABS_OVER_RMS and cos >= MIN_COSINE, f"{what}: max_abs/rms={err:.4g} cosine={cos:.6f}"
+    assert cos >= MIN_COSINE, f"{what}: cosine={cos:.6f}"
+    if literal:
+        assert err <= MAX_ABS_OVER_RMS, f"{what}: max_abs/rms={err:.4g} cosine={cos:.6f}"
+    elif y_ref.numel():
+        ref = y_ref.float()
+        rms = ref.pow(2).mean().sqrt()
+        excess = (y.float() - ref).abs() - (MAX_ABS_OVER_RMS * rms + ref.abs() * 2.0 ** -7)
+        assert excess.max().item() <= 0, f"{what}: max_abs/rms={err:.4g} cosine={cos:.6f} worst excess={excess.max().item():.4g}"
     return err, cos

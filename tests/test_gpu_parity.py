@@ -1,0 +1,263 @@
+"""GPU parity tests (single B200): the CUDA path, called through the megamoe API -> C ABI, against the CPU oracle.
+
+Acceptance bars (written out here because they are the contract):
+  * integer / byte / index results (FP8 codes and scales of the input cast, per-expert counts, token->slot maps,
+    receive-pool rows and metadata, the FP8 recast of the CUDA path's own activations): BIT-EXACT;
+  * layer outputs: max-abs error <= 2e-2 * rms(reference output) and cosine similarity >= 0.999.
+
+Why some checks are stage-isolated: two correct implementations that sum K=4096 products in different orders
+disagree in the last fp32 bit, which now and then flips a bf16 rounding and, more rarely (a few per 100 000
+elements), the FP8 code of an activation.  One flipped top-binade FP8 code changes a single output row by a few
+percent of rms -- the reference's own test allows for the same effect with its absolute tolerance
+(tests/test_mega_moe_dcu.py:729-744).  So large shapes are checked stage by stage (GEMM1 against the oracle within one
+bf16 ulp, requantisation bit-exact on the CUDA path's own activations, GEMM2 + combine against the oracle fed with
+the CUDA path's FP8 activations within the bar), and end to end with the bar on 99.99 % of the elements.
+"""
+import numpy as np
+import pytest
+import torch
+
+import moe_case as mc
+from oracle import moe_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _need_gpu(built_lib):
+    if not torch.cuda.is_available():
+        pytest.fail("these tests need a CUDA device; run them with -m gpu on a B200")
+    from deepgemm_b200 import _lib
+    _lib.lib().mm_set_timeouts(10000, 4000)
+
+
+def _oracle_tail_from_cuda_acts(case, rank, sb, lay):
+    """GEMM2 + combine of the oracle, fed with the FP8 activations and scales the CUDA path produced."""
+    H, I, K = case.H, case.I, case.K
+    n = lay.pool_rows[rank]
+    aq = sb.scratch_view("act_fp8", (sb.pool_rows, I), torch.uint8)[:n].cpu().view(torch.float8_e4m3fn).float()
+    s2 = sb.scratch_view("act_scale", (sb.pool_rows,), torch.float32)[:n].cpu()
+    E_loc = case.E // case.R
+    T = case.tokens[rank]
+    comb = torch.zeros((K, T, H))
+    sr, st, ss = lay.row_src_rank[rank], lay.row_src_token[rank], lay.row_src_slot[rank]
+    for le in range(E_loc):
+        e = rank * E_loc + le
+        cnt = int(lay.totals[e])
+        if not cnt:
+            continue
+        rows = np.arange(lay.pool_off[e], lay.pool_off[e] + cnt)
+        ri = torch.from_numpy(rows)
+        a2 = aq[ri] * s2[ri].view(-1, 1)
+        w2 = case.w2_q[rank][le].float() * case.w2_s[rank][le].view(-1, 1)
+        out = (a2 @ w2.t()).to(torch.bfloat16).float()
+        m = sr[rows] == rank
+        comb[torch.from_numpy(ss[rows][m].astype(np.int64)), torch.from_numpy(st[rows][m].astype(np.int64))] = out[torch.from_numpy(m)]
+    return comb.sum(dim=0).to(torch.bfloat16) if K else comb
+
+
+def _check_case(case, clamp=None, literal_bar=False, **kw):
+    ys, lay, tr = mc.run_oracle(case, clamp, "fused", trace=True)
+    y, sb = mc.run_cuda_rank(case, 0, clamp=clamp, keep=True, **kw)
+    try:
+        f = mc.compare_stages(case, 0, sb, lay, tr, log=lambda *_: None)
+        for key in ("x_q_equal", "x_s_equal", "dest_row_equal", "totals_equal", "pool_off_equal", "plan_rows_equal",
+                    "pool_rows_equal", "pool_meta_equal"):
+            assert f[key], key
+        if case.tokens[0] and lay.totals.sum():
+            n = lay.pool_rows[0]
+            valid = torch.from_numpy(np.nonzero(lay.row_src_rank[0] >= 0)[0])
+            # GEMM1 + SwiGLU: within one bf16 ulp of the oracle, element by element
+            act = sb.scratch_view("act_bf16", (sb.pool_rows, case.I), torch.bfloat16)[:n].cpu().float()[valid]
+            ref = tr.act[0][valid]
+            tol = ref.abs() * 2.0 ** -7 + 1e-30 + ref.abs().amax(dim=1, keepdim=True) * 1e-5
+            assert bool(((act - ref).abs() <= tol).all()), "GEMM1 activations differ by more than one bf16 ulp"
+            # requantisation: bit-exact on the CUDA path's own activations
+            amax = act.abs().amax(dim=1)
+            s2 = (amax / 448.0).clamp(min=1.0e-4)
+            assert torch.equal(sb.scratch_view("act_scale", (sb.pool_rows,), torch.float32)[:n].cpu()[valid], s2)
+            q = (act * (1.0 / s2).view(-1, 1)).to(torch.float8_e4m3fn).view(torch.uint8)
+            assert torch.equal(sb.scratch_view("act_fp8", (sb.pool_rows, case.I), torch.uint8)[:n].cpu()[valid], q)
+            assert f["act_q_mismatch_frac"] < 1e-3
+            # GEMM2 + combine, isolated from upstream tie flips: the literal bar
+            y_tail = _oracle_tail_from_cuda_acts(case, 0, sb, lay)
+            mc.assert_layer_close(y, y_tail, "GEMM2+combine")
+        err, cos = orc.parity_metrics(y, ys[0])
+        assert cos >= mc.MIN_COSINE, cos
+        if literal_bar:
+            assert err <= mc.MAX_ABS_OVER_RMS, err
+        elif y.numel():
+            # end to end against the pure oracle: the bar on 99.99 % of the elements, the rest (rows downstream of a
+            # flipped FP8 tie) within 0.1 * rms
+            rms = ys[0].float().pow(2).mean().sqrt()
+            d = (y.float() - ys[0].float()).abs() / rms
+            assert (d <= mc.MAX_ABS_OVER_RMS).float().mean().item() >= 0.9999 and d.max().item() <= 0.1, (err, cos)
+        return y, ys[0], lay
+    finally:
+        sb.destroy()
+
+
+def test_input_cast_bit_exact_against_reference_fixture():
+    import os
+    import megamoe
+    gold = np.load(os.path.join(os.path.dirname(__file__), "golden", "ref_quant.npz"))
+    x = torch.from_numpy(gold["x_bf16_bits"].copy()).view(torch.bfloat16).cuda()
+    q, s = megamoe.cast_to_fp8_channelwise(x)
+    assert np.array_equal(q.cpu().view(torch.uint8).numpy(), gold["x_q"])
+    assert np.array_equal(s.cpu().numpy(), gold["x_scale"])
+    w1 = torch.from_numpy(gold["w1_bf16_bits"].copy()).view(torch.bfloat16).cuda()
+    w2 = torch.from_numpy(gold["w2_bf16_bits"].copy()).view(torch.bfloat16).cuda()
+    (t1, t1s), (t2, t2s) = megamoe.transform_fp8_weights_for_mega_moe(w1, w2, layout="marlin")
+    assert np.array_equal(t1.cpu().view(torch.uint8).numpy(), gold["t1"]) and np.array_equal(t1s.cpu().numpy(), gold["t1s"])
+    assert np.array_equal(t2.cpu().view(torch.uint8).numpy(), gold["t2"]) and np.array_equal(t2s.cpu().numpy(), gold["t2s"])
+
+
+def test_input_cast_bit_exact_random_and_edges():
+    import megamoe
+    g = torch.Generator().manual_seed(5)
+    x = (torch.randn((777, 4096), generator=g) * torch.logspace(-6, 3, 777).view(-1, 1)).to(torch.bfloat16)
+    x[10] = 0
+    q_ref, s_ref = orc.cast_to_fp8_channelwise(x)
+    q, s = megamoe.cast_to_fp8_channelwise(x.cuda())
+    assert torch.equal(s.cpu(), s_ref)
+    assert torch.equal(q.cpu().view(torch.uint8), q_ref.view(torch.uint8))
+
+
+def test_small_config_literal_bar():
+    """256 tokens, hidden 512, intermediate 256, 8 experts, top-2, seed 0 (the CPU-runnable configuration)."""
+    _check_case(mc.make_case(1, 8, 2, 512, 256, [256], seed=0), literal_bar=True)
+
+
+@pytest.mark.parametrize("clamp", [10.0, 1.0])
+def test_small_config_with_clamp(clamp):
+    _check_case(mc.make_case(1, 8, 2, 512, 256, [256], seed=1), clamp=clamp)
+
+
+def test_invalid_routes_and_ragged_token_count():
+    _check_case(mc.make_case(1, 8, 2, 512, 256, [201], seed=2, invalid_fraction=0.25))
+
+
+def test_zero_tokens():
+    y, ref, lay = _check_case(mc.make_case(1, 8, 2, 512, 256, [0], seed=3), t_max=64)
+    assert y.shape == (0, 512)
+
+
+def test_single_token_and_hidden_not_multiple_of_256():
+    _check_case(mc.make_case(1, 4, 2, 384, 128, [1], seed=4))
+    _check_case(mc.make_case(1, 4, 4, 384, 384, [70], seed=4))
+
+
+def test_skewed_routing_many_blocks_per_expert():
+    # Zipf-skewed popularity: hot experts span several 128-row blocks, cold experts get none
+    _check_case(mc.make_case(1, 16, 4, 512, 256, [1500], seed=5, zipf=True))
+
+
+def test_marlin_weights_and_stats_accumulate():
+    import megamoe
+    case = mc.make_case(1, 8, 2, 512, 256, [128], seed=6)
+    ys, lay, _ = mc.run_oracle(case)
+    stats = torch.randint(0, 100, (8,), dtype=torch.int32, device="cuda")
+    before = stats.clone()
+    y, _ = mc.run_cuda_rank(case, 0, marlin=True, stats=stats)
+    mc.assert_layer_close(y, ys[0], "marlin")
+    # the reference test's rule: stats == initial + bincount of valid experts (tests/test_mega_moe_dcu.py:735-739)
+    assert torch.equal(stats.cpu(), before.cpu() + torch.from_numpy(lay.totals.astype(np.int32)))
+
+
+def test_plain_layout_weights_and_host_quantised_inputs():
+    """Weights handed over as plain [E, rows, K] tensors (re-packed once by the API) and inputs quantised on the host."""
+    import megamoe
+    case = mc.make_case(1, 8, 2, 512, 256, [100], seed=13)
+    y, _ = mc.run_cuda_rank(case, 0, quantise_on_device=False)
+    mc.assert_layer_close(y, mc.run_oracle(case)[0][0], "plain-layout weights")
+    w = case.w1_q[0].cuda()
+    assert torch.equal(megamoe.unpack_weights_tiled(megamoe.pack_weights_tiled(w)).view(torch.uint8), w.view(torch.uint8))
+
+
+def test_buffer_reuse_is_deterministic_and_self_cleaning():
+    a = mc.make_case(1, 8, 2, 512, 256, [256], seed=7)
+    b = mc.make_case(1, 8, 2, 512, 256, [33], seed=8)
+    ya, sb = mc.run_cuda_rank(a, 0, keep=True, t_max=256)
+    yb, _ = mc.run_cuda_rank(b, 0, sb=sb)
+    ya2, _ = mc.run_cuda_rank(a, 0, sb=sb)
+    sb.destroy()
+    assert torch.equal(ya.view(torch.int16), ya2.view(torch.int16))
+    mc.assert_layer_close(yb, mc.run_oracle(b)[0][0], "second case on a reused buffer")
+
+
+def test_weight_scaling_and_token_permutation_properties():
+    """Size-independent properties: doubling every route weight doubles y exactly (powers of two commute with every
+    rounding on the path), and permuting the tokens permutes y bit for bit."""
+    case = mc.make_case(1, 8, 2, 512, 256, [200], seed=9)
+    y, sb = mc.run_cuda_rank(case, 0, keep=True)
+    case.w[0] = case.w[0] * 2
+    y2, _ = mc.run_cuda_rank(case, 0, sb=sb)
+    assert torch.equal((y.float() * 2).to(torch.bfloat16).view(torch.int16), y2.view(torch.int16))
+    perm = torch.randperm(200, generator=torch.Generator().manual_seed(1))
+    case.x_bf16[0] = case.x_bf16[0][perm]; case.idx[0] = case.idx[0][perm]; case.w[0] = case.w[0][perm]
+    y3, _ = mc.run_cuda_rank(case, 0, sb=sb)
+    sb.destroy()
+    assert torch.equal(y2[perm].view(torch.int16), y3.view(torch.int16))
+
+
+def test_dsv4_shaped_slice():
+    """hidden 4096 / intermediate 2048 / top-6 on 16 experts: the flagship tile shapes at an oracle-friendly size."""
+    _check_case(mc.make_case(1, 16, 6, 4096, 2048, [512], seed=10))
+
+
+def test_api_argument_errors():
+    import megamoe
+    case = mc.make_case(1, 8, 2, 512, 256, [16], seed=11)
+    sb = megamoe.get_symm_buffer_for_mega_moe(None, 8, 16, 2, 512, 256)
+    assert sb.num_max_tokens_per_rank == 384 and sb.cuda_graph_max_tokens_per_rank == 16
+    l1, l2 = megamoe.transform_fp8_weights_for_mega_moe(case.w1_bf16[0].cuda(), case.w2_bf16[0].cuda())
+    y = torch.empty((16, 512), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(ValueError):
+        megamoe.fp8_mega_moe(y, l1, l2, sb, big_fused_cuda_graph=True, stages_fused_cuda_graph=True)
+    with pytest.raises(RuntimeError):
+        megamoe.fp8_mega_moe(y, l1, l2, sb, recipe=(1, 1, 128))
+    with pytest.raises(RuntimeError):
+        megamoe.fp8_mega_moe(y, l1, l2, sb, activation="gelu")
+    with pytest.raises(RuntimeError):
+        megamoe.fp8_mega_moe(y, l1, l2, sb, fast_math=False)
+    with pytest.raises(ValueError):
+        megamoe.fp8_mega_moe(y, l1, l2, sb, dispatch_num_tokens=10 ** 6)
+    with pytest.raises(ValueError):   # more rows than the buffer holds: rejected like the reference (megamoe/__init__.py:399-404)
+        megamoe.fp8_mega_moe(torch.empty((500, 512), dtype=torch.bfloat16, device="cuda"), l1, l2, sb)
+    with pytest.raises(RuntimeError):
+        megamoe.fp8_mega_moe(y.float(), l1, l2, sb)
+    with pytest.raises(ValueError):   # graph mode needs a bucket-sized y and forbids stats
+        megamoe.fp8_mega_moe(y[:8], l1, l2, sb, big_fused_cuda_graph=True)
+    with pytest.raises(ValueError):
+        megamoe.fp8_mega_moe(y, l1, l2, sb, big_fused_cuda_graph=True,
+                             cumulative_local_expert_recv_stats=torch.zeros(8, dtype=torch.int32, device="cuda"))
+    sb.destroy()
+
+
+def test_graph_bucket_mode_uses_device_side_token_count():
+    """CUDA-graph bucket semantics (README 'CUDA Graph' section of the reference; tests/test_mega_moe_dcu.py:563-715):
+    the call is captured once for the bucket size and replayed with different device-side token counts."""
+    import megamoe
+    case = mc.make_case(1, 8, 2, 512, 256, [96], seed=12)
+    ys, _, _ = mc.run_oracle(case)
+    sb = megamoe.get_symm_buffer_for_mega_moe(None, 8, 96, 2, 512, 256)
+    l1, l2 = megamoe.transform_fp8_weights_for_mega_moe(case.w1_bf16[0].cuda(), case.w2_bf16[0].cuda())
+    xq, xs = megamoe.cast_to_fp8_channelwise(case.x_bf16[0].cuda())
+    sb.x[:96].copy_(xq); sb.x_sf[:96].copy_(xs)
+    sb.topk_idx[:96].copy_(case.idx[0].cuda()); sb.topk_weights[:96].copy_(case.w[0].cuda())
+    y = torch.zeros((96, 512), dtype=torch.bfloat16, device="cuda")
+    megamoe.fp8_mega_moe(y, l1, l2, sb, stages_fused_cuda_graph=True)   # warm-up outside capture
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        megamoe.fp8_mega_moe(y, l1, l2, sb, stages_fused_cuda_graph=True)
+    for n in (96, 40, 0, 77):
+        y.fill_(7.0)
+        sb.cuda_graph_num_tokens.fill_(n)
+        graph.replay()
+        torch.cuda.synchronize()
+        sb.check_status()
+        if n:
+            mc.assert_layer_close(y[:n].cpu(), ys[0][:n], f"graph replay with {n} tokens")
+        assert bool((y[n:] == 7.0).all()), "rows past the device-side token count must not be written"
+    sb.destroy()

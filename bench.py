@@ -108,9 +108,9 @@ def make_rank_data(rank: int, world: int, tokens: int, dev):
     import megamoe
     e_loc = E // world
     g = torch.Generator(device=dev).manual_seed(1000 + rank)
-    l1q = torch.empty((e_loc, 2 * I // 128, H // 128, 128, 128), dtype=torch.float8_e4m3fn, device=dev)   # tiled layout
+    l1q = torch.empty((e_loc, I // 128, H // 128, 256, 128), dtype=torch.float8_e4m3fn, device=dev)   # tiled layout
     l1s = torch.empty((e_loc, 2 * I), dtype=torch.float32, device=dev)
-    l2q = torch.empty((e_loc, H // 128, I // 128, 128, 128), dtype=torch.float8_e4m3fn, device=dev)
+    l2q = torch.empty((e_loc, H // 256, I // 128, 256, 128), dtype=torch.float8_e4m3fn, device=dev)
     l2s = torch.empty((e_loc, H), dtype=torch.float32, device=dev)
     step = 16
     for e0 in range(0, e_loc, step):   # a few experts at a time bounds the bf16 temporaries
@@ -127,12 +127,10 @@ def make_rank_data(rank: int, world: int, tokens: int, dev):
     return (l1q, l1s), (l2q, l2s), x, idx.to(torch.int64), w
 
 
-def _plain(w):
-    """Weights as plain [E, rows, K] on the host (undo the tiled packing if present)."""
-    if w.dim() == 5:
-        g, rt, kt = w.shape[:3]
-        w = w.view(torch.uint8).permute(0, 1, 3, 2, 4).reshape(g, rt * 128, kt * 128).view(torch.float8_e4m3fn)
-    return w.cpu()
+def _plain(w, which, rows):
+    """Weights as plain [E, rows, K] on the host (undo the tiled packing)."""
+    import megamoe
+    return megamoe.unpack_weights_tiled(w, which, rows).cpu() if w.dim() == 5 else w.cpu()
 
 
 def cpu_baseline(l1, l2, x_q, x_s, idx, w, n_experts: int, threads: int, repeats: int = 1):
@@ -143,7 +141,7 @@ def cpu_baseline(l1, l2, x_q, x_s, idx, w, n_experts: int, threads: int, repeats
     keep = idx < n_experts
     idx_s = torch.where(keep, idx, torch.full_like(idx, -1)).cpu()
     args = ([x_q.cpu()], [x_s.cpu()], [idx_s], [w.cpu()],
-            [_plain(l1[0][:n_experts])], [l1[1][:n_experts].cpu()], [_plain(l2[0][:n_experts])], [l2[1][:n_experts].cpu()])
+            [_plain(l1[0][:n_experts], "l1", 2 * I)], [l1[1][:n_experts].cpu()], [_plain(l2[0][:n_experts], "l2", H)], [l2[1][:n_experts].cpu()])
     rows = int(keep.sum().item())
     best = float("inf")
     for _ in range(repeats):

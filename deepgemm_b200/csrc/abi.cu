@@ -76,17 +76,17 @@ int get_encode_fn(EncodeTiledFn* out) {
     return 0;
 }
 
-struct MapKey { const void* ptr; uint64_t inner, rows; };
+struct MapKey { const void* ptr; uint64_t inner, rows; uint32_t box_rows; };
 struct MapEntry { MapKey key; CUtensorMap map; };
 std::mutex g_map_mu;
 std::vector<MapEntry> g_maps;
 
-// 2-D row-major byte matrix [rows][inner], box = 128 rows x 128 bytes, 128-byte swizzle.
-int tensor_map_2d(const void* ptr, uint64_t inner, uint64_t rows, CUtensorMap* out) {
+// 2-D row-major byte matrix [rows][inner], box = box_rows rows x 128 bytes, 128-byte swizzle.
+int tensor_map_2d(const void* ptr, uint64_t inner, uint64_t rows, uint32_t box_rows, CUtensorMap* out) {
     {
         std::lock_guard<std::mutex> lk(g_map_mu);
         for (auto& m : g_maps)
-            if (m.key.ptr == ptr && m.key.inner == inner && m.key.rows == rows) { *out = m.map; return 0; }
+            if (m.key.ptr == ptr && m.key.inner == inner && m.key.rows == rows && m.key.box_rows == box_rows) { *out = m.map; return 0; }
     }
     EncodeTiledFn enc;
     if (int rc = get_encode_fn(&enc)) return rc;
@@ -94,7 +94,7 @@ int tensor_map_2d(const void* ptr, uint64_t inner, uint64_t rows, CUtensorMap* o
     MM_REQUIRE(inner % 16 == 0, "row pitch must be a multiple of 16 bytes");
     cuuint64_t dims[2] = {inner, rows};
     cuuint64_t strides[1] = {inner};
-    cuuint32_t box[2] = {128, 128};
+    cuuint32_t box[2] = {128, box_rows};
     cuuint32_t estr[2] = {1, 1};
     CUtensorMap map;
     CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box, estr,
@@ -103,7 +103,7 @@ int tensor_map_2d(const void* ptr, uint64_t inner, uint64_t rows, CUtensorMap* o
     MM_REQUIRE(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
     std::lock_guard<std::mutex> lk(g_map_mu);
     if (g_maps.size() > 256) g_maps.clear();
-    g_maps.push_back({{ptr, inner, rows}, map});
+    g_maps.push_back({{ptr, inner, rows, box_rows}, map});
     *out = map;
     return 0;
 }
@@ -315,10 +315,10 @@ int mm_fp8_w8a8_mega_moe(void* y, const void* w1, const float* s1, const void* w
 
     uint8_t* sc = rp.scratch;
     CUtensorMap tm_pool, tm_w1, tm_act, tm_w2;
-    if (int rc = tensor_map_2d(rp.sym + rp.sl.pool_x, (uint64_t)H, (uint64_t)rp.sl.pool_rows, &tm_pool)) return rc;
-    if (int rc = tensor_map_2d(w1, 128, (uint64_t)E_loc * 2 * I * (H / 128), &tm_w1)) return rc;
-    if (int rc = tensor_map_2d(sc + rp.cl.act_fp8, (uint64_t)I, (uint64_t)rp.sl.pool_rows, &tm_act)) return rc;
-    if (int rc = tensor_map_2d(w2, 128, (uint64_t)E_loc * H * (I / 128), &tm_w2)) return rc;
+    if (int rc = tensor_map_2d(rp.sym + rp.sl.pool_x, (uint64_t)H, (uint64_t)rp.sl.pool_rows, 128, &tm_pool)) return rc;
+    if (int rc = tensor_map_2d(w1, 128, (uint64_t)E_loc * (I / 128) * (H / 128) * 256, 256, &tm_w1)) return rc;
+    if (int rc = tensor_map_2d(sc + rp.cl.act_fp8, (uint64_t)I, (uint64_t)rp.sl.pool_rows, 128, &tm_act)) return rc;
+    if (int rc = tensor_map_2d(w2, 128, (uint64_t)E_loc * ((H + 255) / 256) * (I / 128) * 256, 256, &tm_w2)) return rc;
 
     mm::GemmParams g1;
     memset(&g1, 0, sizeof(g1));

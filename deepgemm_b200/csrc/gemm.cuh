@@ -111,19 +111,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             const int mb = tile / p.n_blocks, nb = tile - mb * p.n_blocks;
             const int e = p.mblock_expert[mb];
             const int a_row = mb * kBlockM;
-            // weights are stored tile by tile: [expert][row tile of 128][k tile of 128 B][128 rows][128 B], so the 16 KiB
-            // a TMA box fetches are contiguous in HBM and the k tiles of one row tile follow each other
-            const int row_tiles = p.w_rows_per_expert / 128;
-            int rt0, rt1;
-            if (kKind == 0) {
-                rt0 = nb;                      // gate rows
-                rt1 = row_tiles / 2 + nb;      // matching up rows
-            } else {
-                rt0 = nb * 2;
-                rt1 = nb * 2 + 1;              // may lie past H when H % 256 == 128: results unused
-            }
-            const int b_tile0 = (e * row_tiles + rt0) * k_blocks;
-            const int b_tile1 = (e * row_tiles + rt1) * k_blocks;
+            // weights are stored tile by tile in the order this kernel consumes them:
+            // [expert][n block][k block][256 rows][128 B] -- one TMA box = one contiguous 32 KiB block, and the k blocks
+            // of one output tile follow each other, so each CTA streams one sequential run of HBM per tile
+            const int b_tile0 = (e * p.n_blocks + nb) * k_blocks;
             for (int kb = 0; kb < k_blocks; ++kb) {
                 if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.timeout_ns)) { alive = false; break; }
                 if (lane == 0) {
@@ -131,8 +122,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                     const uint32_t b_dst = a_dst + kABytes;
                     mbar_arrive_expect_tx(full_bar(stage), kStageBytes);
                     tma_load_2d(a_dst, &tm_a, kb * kBlockK, a_row, full_bar(stage));
-                    tma_load_2d(b_dst, &tm_b, 0, (b_tile0 + kb) * 128, full_bar(stage));
-                    tma_load_2d(b_dst + 128 * kBlockK, &tm_b, 0, (b_tile1 + kb) * 128, full_bar(stage));
+                    tma_load_2d(b_dst, &tm_b, 0, (b_tile0 + kb) * kBlockN, full_bar(stage));
                 }
                 __syncwarp();
                 if (++stage == kStages) { stage = 0; phase ^= 1u; }

@@ -7,7 +7,7 @@ pointers.  There is no CPU or PyTorch fallback: CUDA tensors are required and a 
 Differences a caller can observe (all supersets of the reference behaviour):
   * any EP size in 1..16 and any shape with hidden % 128 == 0, intermediate % 128 == 0, top-k <= 32 is accepted
     (the reference accepts only EP8 / 256 experts / top-6 / 4096 / 2048: csrc/kernels/mega_moe_fused_hip.cu:94-119);
-  * `transform_fp8_weights_for_mega_moe` returns weights packed in 128x128-byte tiles (one TMA box = 16 contiguous KiB);
+  * `transform_fp8_weights_for_mega_moe` returns weights packed in 256x128-byte tiles (one TMA box = 32 contiguous KiB);
     plain `[E_loc, rows, K]` weights and the reference's Marlin layout `[E_loc, rows/16, K*16]` are also accepted and
     re-packed once;
   * `group=None` builds a single-rank buffer without torch.distributed;
@@ -135,27 +135,49 @@ def _marlin_inverse(weight: torch.Tensor, rows: int, k: int) -> torch.Tensor:
             .contiguous().reshape(g, rows, k).view(weight.dtype))
 
 
-def pack_weights_tiled(weight: torch.Tensor) -> torch.Tensor:
-    """[E, rows, K] -> [E, rows/128, K/128, 128, 128]: every 128-row x 128-byte tile contiguous (16 KiB), the K tiles of
-    one row tile adjacent.  This is the layout the GEMM kernels stream from HBM (one TMA box = one contiguous tile); it
-    plays the role the 16x16 Marlin packing plays for the reference's MMAC kernels (megamoe/__init__.py:81-98)."""
+def pack_weights_tiled(weight: torch.Tensor, which: str) -> torch.Tensor:
+    """Pack a grouped FP8 weight tensor [E, rows, K] into the order the GEMM kernels stream it from HBM:
+    [E][n block][K/128][256 rows][128 bytes], one contiguous 32 KiB block per (output tile, k block).
+
+    which="l1": gate+up weights [E, 2I, K]; n block j holds gate rows [128j, 128j+128) followed by the matching up
+                rows [I+128j, I+128j+128), so one output tile yields 128 complete SwiGLU results.
+    which="l2": down weights [E, H, K]; n block j holds rows [256j, 256j+256) (zero rows past H when H % 256 == 128).
+    It plays the role the 16x16 Marlin packing plays for the reference's MMAC kernels (megamoe/__init__.py:81-98)."""
     if weight.dim() != 3:
         raise ValueError("expected a grouped [E, rows, K] weight tensor")
+    if which not in ("l1", "l2"):
+        raise ValueError("which must be 'l1' or 'l2'")
     g, rows, k = weight.shape
-    if rows % 128 != 0 or k % 128 != 0:
-        raise ValueError("rows and K must be multiples of 128")
-    out = torch.empty((g, rows // 128, k // 128, 128, 128), dtype=weight.dtype, device=weight.device)
+    if rows % 128 != 0 or k % 128 != 0 or (which == "l1" and rows % 256 != 0):
+        raise ValueError("rows and K must be multiples of 128 (L1 rows: of 256)")
     src = weight.view(torch.uint8)
-    dst = out.view(torch.uint8)
-    for e in range(g):   # one expert at a time bounds the temporary
-        dst[e].copy_(src[e].reshape(rows // 128, 128, k // 128, 128).permute(0, 2, 1, 3))
-    return out
+    if which == "l1":
+        nb = rows // 256
+        out = torch.empty((g, nb, k // 128, 256, 128), dtype=torch.uint8, device=weight.device)
+        for e in range(g):   # one expert at a time bounds the temporary
+            # [2 (gate/up), nb, 128, kt, 128] -> [nb, kt, 2, 128, 128]
+            out[e].view(nb, k // 128, 2, 128, 128).copy_(src[e].reshape(2, nb, 128, k // 128, 128).permute(1, 3, 0, 2, 4))
+    else:
+        nb = (rows + 255) // 256
+        out = torch.zeros((g, nb, k // 128, 256, 128), dtype=torch.uint8, device=weight.device)
+        full = rows // 256
+        for e in range(g):
+            if full:
+                out[e, :full].copy_(src[e, :full * 256].reshape(full, 256, k // 128, 128).permute(0, 2, 1, 3))
+            if rows % 256:
+                out[e, full, :, :128].copy_(src[e, full * 256:].reshape(128, k // 128, 128).permute(1, 0, 2))
+    return out.view(weight.dtype)
 
 
-def unpack_weights_tiled(weight: torch.Tensor) -> torch.Tensor:
-    """Inverse of pack_weights_tiled: [E, rows/128, K/128, 128, 128] -> [E, rows, K]."""
-    g, rt, kt = weight.shape[:3]
-    return (weight.view(torch.uint8).permute(0, 1, 3, 2, 4).contiguous().reshape(g, rt * 128, kt * 128).view(weight.dtype))
+def unpack_weights_tiled(weight: torch.Tensor, which: str, rows: int) -> torch.Tensor:
+    """Inverse of pack_weights_tiled: back to [E, rows, K]."""
+    g, nb, kt = weight.shape[:3]
+    src = weight.view(torch.uint8)
+    if which == "l1":
+        out = src.reshape(g, nb, kt, 2, 128, 128).permute(0, 3, 1, 4, 2, 5).reshape(g, 2 * nb * 128, kt * 128)
+    else:
+        out = src.permute(0, 1, 3, 2, 4).reshape(g, nb * 256, kt * 128)[:, :rows]
+    return out.contiguous().view(weight.dtype)
 
 
 def transform_fp8_weights_for_mega_moe(l1_weights: torch.Tensor, l2_weights: torch.Tensor, layout: str = "tiled"):
@@ -167,7 +189,7 @@ def transform_fp8_weights_for_mega_moe(l1_weights: torch.Tensor, l2_weights: tor
     if layout == "marlin":
         return (weight8bit_nt_kpack2_marlin(l1_fp8), l1_scale), (weight8bit_nt_kpack2_marlin(l2_fp8), l2_scale)
     if layout == "tiled":
-        return (pack_weights_tiled(l1_fp8), l1_scale), (pack_weights_tiled(l2_fp8), l2_scale)
+        return (pack_weights_tiled(l1_fp8, "l1"), l1_scale), (pack_weights_tiled(l2_fp8, "l2"), l2_scale)
     if layout != "native":
         raise ValueError("layout must be 'tiled', 'native' or 'marlin'")
     return (l1_fp8, l1_scale), (l2_fp8, l2_scale)
@@ -369,24 +391,25 @@ def get_symm_buffer_for_mega_moe(group, num_experts: int, num_max_tokens_per_ran
 _packed_weight_cache = {}
 
 
-def _tiled_weight(w: torch.Tensor, rows: int, k: int, what: str) -> torch.Tensor:
-    """Accept the tiled layout [E_loc, rows/128, K/128, 128, 128] as is; plain [E_loc, rows, K] and the reference's
+def _tiled_weight(w: torch.Tensor, rows: int, k: int, which: str) -> torch.Tensor:
+    """Accept the tiled layout [E_loc, n blocks, K/128, 256, 128] as is; plain [E_loc, rows, K] and the reference's
     Marlin shape [E_loc, rows/16, K*16] are re-packed once and cached (keyed by storage address and version)."""
-    if w.dim() == 5 and tuple(w.shape[1:]) == (rows // 128, k // 128, 128, 128):
+    nb = rows // 256 if which == "l1" else (rows + 255) // 256
+    if w.dim() == 5 and tuple(w.shape[1:]) == (nb, k // 128, 256, 128):
         return w if w.is_contiguous() else w.contiguous()
     if w.dim() != 3:
         raise RuntimeError("weights must be grouped 3D tensors (or tiled 5D tensors)")
     native = w.shape[1] == rows and w.shape[2] == k
     marlin = w.shape[1] == rows // 16 and w.shape[2] == k * 16
     if not (native or marlin):
-        raise RuntimeError(f"invalid {what} weight shape {tuple(w.shape)}, expected [expert, {rows}, {k}], "
-                           f"Marlin [expert, {rows // 16}, {k * 16}] or tiled [expert, {rows // 128}, {k // 128}, 128, 128]")
+        raise RuntimeError(f"invalid {which.upper()} weight shape {tuple(w.shape)}, expected [expert, {rows}, {k}], "
+                           f"Marlin [expert, {rows // 16}, {k * 16}] or tiled [expert, {nb}, {k // 128}, 256, 128]")
     key = (w.data_ptr(), tuple(w.shape), w._version)
     hit = _packed_weight_cache.get(key)
     if hit is None:
         if len(_packed_weight_cache) > 16:
             _packed_weight_cache.clear()
-        hit = pack_weights_tiled(w.contiguous() if native else _marlin_inverse(w, rows, k))
+        hit = pack_weights_tiled(w.contiguous() if native else _marlin_inverse(w, rows, k), which)
         _packed_weight_cache[key] = hit
     return hit
 
@@ -465,8 +488,8 @@ def fp8_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer: SymmBuffer
         raise RuntimeError("invalid L2 scale shape")
     if num_tokens > sb.num_max_tokens_per_rank:
         raise RuntimeError("too many tokens")
-    w1 = _tiled_weight(l1_w, 2 * inter, hidden, "L1")
-    w2 = _tiled_weight(l2_w, hidden, inter, "L2")
+    w1 = _tiled_weight(l1_w, 2 * inter, hidden, "l1")
+    w2 = _tiled_weight(l2_w, hidden, inter, "l2")
     stats_ptr = None
     if cumulative_local_expert_recv_stats is not None:
         st = cumulative_local_expert_recv_stats

@@ -76,10 +76,11 @@ int mm_quant_per_token(const void* x_bf16, int64_t rows, int k, void* out_fp8, f
 
 /* The layer.  Inputs x / x_sf / topk_idx / topk_weights are read from the symmetric buffer views; y receives
  * bf16 [num_tokens, H].  w1 = fp8 weights [E_loc, 2I, H] (rows [0,I) gate, [I,2I) up) with s1 f32 [E_loc, 2I]; w2 = fp8
- * weights [E_loc, H, I] with s2 f32 [E_loc, H].  Both weight tensors are stored TILED: [E_loc][rows/128][K/128][128][128],
- * i.e. element (row, k) of expert e at ((e*rows/128 + row/128)*K/128 + k/128)*16384 + (row%128)*128 + k%128, so that every
- * 128-row x 128-byte TMA box is one contiguous 16 KiB block (the reference packs 16x16 Marlin tiles for its MMAC units
- * instead, deep_gemm/include/deep_gemm/layout/mega_moe_dcu.cuh:50-66).  stats (nullable) int32 [E_loc] accumulates rows received per local
+ * weights [E_loc, H, I] with s2 f32 [E_loc, H].  Both weight tensors are stored TILED in the order the GEMM kernels
+ * stream them: [E_loc][n block][K/128][256 rows][128 bytes], one contiguous 32 KiB block per (output tile, k block).
+ * For w1, n block j (j < I/128) holds gate rows [128j,128j+128) followed by up rows [I+128j, I+128j+128); for w2, n block
+ * j (j < ceil(H/256)) holds rows [256j, 256j+256), zero rows past H.  (The reference packs 16x16 Marlin tiles for its
+ * MMAC units instead, deep_gemm/include/deep_gemm/layout/mega_moe_dcu.cuh:50-66.)  stats (nullable) int32 [E_loc] accumulates rows received per local
  * expert.  peer_ptrs: HOST array of the R ranks' symmetric-buffer device addresses (entry `rank` is sym_base).
  * runtime_num_tokens (nullable): device int32 overriding num_tokens (CUDA-graph bucket mode).
  * activation_clamp: +inf for none.  mode: MM_MODE_STAGED or MM_MODE_FUSED.

@@ -174,3 +174,22 @@ def assert_layer_close(y: torch.Tensor, y_ref: torch.Tensor, what="", literal=Fa
         excess = (y.float() - ref).abs() - (MAX_ABS_OVER_RMS * rms + ref.abs() * 2.0 ** -7)
         assert excess.max().item() <= 0, f"{what}: max_abs/rms={err:.4g} cosine={cos:.6f} worst excess={excess.max().item():.4g}"
     return err, cos
+
+
+def assert_end_to_end_close(y: torch.Tensor, y_ref: torch.Tensor, what=""):
+    """End-to-end comparison with the pure oracle on shapes where FP8 tie flips occur (see test_gpu_parity.py):
+    cosine >= 0.999; every element within 0.1 * rms; and the per-element bar (2e-2 * rms + one bf16 ulp) on all but a
+    few rows -- a flipped top-binade FP8 activation code moves ONE output row by a few percent of rms, and a token has
+    K * I such codes, so up to 5 % of the rows may carry one."""
+    assert y.shape == y_ref.shape
+    if y_ref.numel() == 0:
+        return
+    assert not torch.isnan(y.float()).any(), f"{what}: NaN in output"
+    ref = y_ref.float()
+    rms = ref.pow(2).mean().sqrt()
+    err, cos = orc.parity_metrics(y, y_ref)
+    assert cos >= MIN_COSINE, f"{what}: cosine={cos:.6f}"
+    d = (y.float() - ref).abs()
+    assert (d / rms).max().item() <= 0.1, f"{what}: max_abs/rms={err:.4g}"
+    bad_rows = ((d - (MAX_ABS_OVER_RMS * rms + ref.abs() * 2.0 ** -7)) > 0).any(dim=1).float().mean().item()
+    assert bad_rows <= 0.05, f"{what}: {bad_rows:.3%} of the rows exceed the per-element bar (max_abs/rms={err:.4g})"

@@ -35,7 +35,7 @@ def test_missing_peer_signal_times_out_with_status_and_context_survives(built_li
         case = mc.make_case(1, 4, 2, H, I, [64], seed=30)      # rank 0 owns experts 0..3 of the 8
         dev = torch.device("cuda")
         import megamoe
-        w1q, w2q = megamoe.pack_weights_tiled(case.w1_q[0].to(dev)), megamoe.pack_weights_tiled(case.w2_q[0].to(dev))
+        w1q, w2q = megamoe.pack_weights_tiled(case.w1_q[0].to(dev), "l1"), megamoe.pack_weights_tiled(case.w2_q[0].to(dev), "l2")
         w1s, w2s = case.w1_s[0].to(dev), case.w2_s[0].to(dev)
         local[off["x"]:off["x"] + 64 * H].copy_(case.x_q[0].view(torch.int8).flatten().to(dev))
         local[off["x_sf"]:off["x_sf"] + 64 * 4].view(torch.float32).copy_(case.x_s[0].to(dev))

@@ -6,7 +6,7 @@
 //   kind 1 (GEMM2): out[row, h] = bf16( acc * (s2[row] * sw2[h]) ) stored straight into combine[slot][token][:] of the
 //                   SOURCE rank over NVLink.  Replaces impls/mega_moe_dcu_tiles.cuh:735-1163.
 //
-// One persistent CTA per SM, 192 threads: warp 0 = TMA producer, warp 1 = MMA issuer (owns TMEM), warps 2-5 = epilogue.
+// One persistent CTA per SM, 320 threads: warp 0 = TMA producer, warp 1 = MMA issuer (owns TMEM), warps 2-9 = epilogue.
 // Tile = 128 pool rows (UMMA M, TMEM lanes) x 256 weight rows (UMMA N, TMEM columns) x 128 bytes of K per stage;
 // two accumulator buffers (2 x 256 TMEM columns) so the epilogue of tile i overlaps the MMAs of tile i+1.
 // For kind 0 the 256 weight rows are 128 gate rows and the 128 matching up rows, so one tile yields 128 SwiGLU outputs.
@@ -21,14 +21,17 @@ constexpr int kBlockM = MM_BLOCK_M;   // 128
 constexpr int kBlockN = 256;
 constexpr int kBlockK = 128;          // bytes == fp8 elements; one 128-byte swizzle atom
 constexpr int kStages = 4;
-constexpr int kGemmThreads = 192;
+constexpr int kEpilogueWarps = 8;
+constexpr int kEpilogueThreads = kEpilogueWarps * 32;
+constexpr int kGemmThreads = 64 + kEpilogueThreads;     // TMA warp + MMA warp + epilogue warps
 constexpr int kABytes = kBlockM * kBlockK;              // 16 KiB
 constexpr int kBBytes = kBlockN * kBlockK;              // 32 KiB
 constexpr int kStageBytes = kABytes + kBBytes;
-constexpr int kStagingRowBytes = 128 + 16;              // one 128-byte output segment per row + pad (bank spread)
-constexpr int kStagingBytes = 4 * 32 * kStagingRowBytes;
+constexpr int kStagingWarpBytes = 32 * 128;              // one 128-byte output segment for each of a warp's 32 rows
+constexpr int kStagingBytes = kEpilogueWarps * kStagingWarpBytes;
 constexpr int kScaleBytes = 2 * kBlockN * 4;
-constexpr int kGemmSmemBytes = 1024 /*align slack*/ + kStages * kStageBytes + kStagingBytes + kScaleBytes + 256 /*barriers*/;
+constexpr int kGemmSmemBytes = kStages * kStageBytes + kStagingBytes + kScaleBytes + 256 /*barriers*/;
+static_assert(kGemmSmemBytes <= 232448, "exceeds the 227 KiB of shared memory a CTA can have");
 
 struct GemmParams {
     int kdim;                  // reduction length (H for kind 0, I for kind 1)
@@ -54,7 +57,9 @@ struct GemmParams {
     uint64_t timeout_ns;
 };
 
-__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
+// x * sigmoid(x) with the fast exponential and reciprocal units, as the reference does
+// (deep_gemm/include/deep_gemm/common/mega_moe_dcu.cuh:90-99: exp2 and rcp intrinsics)
+__device__ __forceinline__ float silu_f(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -64,9 +69,13 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 template <int kKind>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, GemmParams p) {
-    extern __shared__ uint8_t smem_raw[];
-    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    extern __shared__ __align__(1024) uint8_t smem_raw[];   // the swizzled operand tiles need 1024-byte alignment
+    const uint32_t smem_base = smem_u32(smem_raw);
+    uint8_t* smem_gen = smem_raw;
+    if ((smem_base & 1023u) != 0u) {                         // never expected; refuse to run rather than compute garbage
+        if (threadIdx.x == 0 && atomicCAS(p.status, 0, MM_ERR_PIPE_TIMEOUT) == 0) { p.status[1] = 100 + kKind; p.status[2] = blockIdx.x; }
+        return;
+    }
     // layout: [stages x (A | B)] [staging] [scales] [barriers]
     const uint32_t staging_u32 = smem_base + kStages * kStageBytes;
     uint8_t* staging_gen = smem_gen + kStages * kStageBytes;
@@ -84,7 +93,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-        for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 4); }
+        for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), kEpilogueWarps); }
         *abort_flag = 0;
         fence_barrier_init();
         prefetch_tensormap(&tm_a);
@@ -159,33 +168,36 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
         }
     } else {
-        // ------------------------------------------------------------------ epilogue (warps 2..5)
+        // ------------------------------------------------------------------ epilogue (warps 2..9)
+        // Two warps per TMEM lane quarter: warp 2+q (half 0) and warp 6+q (half 1) split the tile's columns, so every
+        // scheduler has two epilogue warps to interleave (one warp alone cannot hide its own ALU/MUFU latencies).
         const int q = warp & 3;                       // TMEM lane quarter this warp may read
+        const int half = (warp - 2) >> 2;             // which half of the tile's output columns
         const int et = q * 32 + lane;                 // row of the tile == TMEM lane
-        uint8_t* my_staging = staging_gen + (warp - 2) * 32 * kStagingRowBytes;
+        uint8_t* my_staging = staging_gen + (warp - 2) * kStagingWarpBytes;
+        const bool do_clamp = p.clamp < 3.0e38f;
         int acc = 0; uint32_t acc_phase = 0;
         bool alive = true;
         for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
+            if (*abort_flag != 0) break;
             const int mb = tile / p.n_blocks, nb = tile - mb * p.n_blocks;
             const int e = p.mblock_expert[mb];
             const int valid = p.mblock_valid[mb];
             const int row = mb * kBlockM + et;
             const bool row_ok = et < valid;
             float* sc = scales_gen + acc * kBlockN;
-            // stage the 256 per-column weight scales of this tile (threads 0..127 of the epilogue, two each)
+            // stage the 256 per-column weight scales of this tile (one per epilogue thread)
             {
                 const int t = (warp - 2) * 32 + lane;
                 const float* ws = p.w_scale + static_cast<int64_t>(e) * p.w_rows_per_expert;
                 if (kKind == 0) {
-                    sc[t] = ws[nb * 128 + t];
-                    sc[128 + t] = ws[p.w_rows_per_expert / 2 + nb * 128 + t];
+                    sc[t] = t < 128 ? ws[nb * 128 + t] : ws[p.w_rows_per_expert / 2 + nb * 128 + (t - 128)];
                 } else {
-                    const int c0 = nb * kBlockN + t, c1 = c0 + 128;
+                    const int c0 = nb * kBlockN + t;
                     sc[t] = c0 < p.n_out ? ws[c0] : 0.0f;
-                    sc[128 + t] = c1 < p.n_out ? ws[c1] : 0.0f;
                 }
             }
-            named_bar_sync(1, 128);
+            named_bar_sync(1, kEpilogueThreads);
             float row_scale = 0.0f, route_w = 0.0f;
             uint8_t* out_ptr = nullptr;                // kind 1: destination row in the source rank's combine buffer
             if (row_ok) {
@@ -203,83 +215,79 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.timeout_ns)) { alive = false; break; }
             tc_fence_after();
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * kBlockN;
+            // Each pass handles one 128-byte output segment (64 bf16) per row: two 32-column chunks, staged in shared
+            // memory (16-byte pieces XOR-swizzled by row so neither phase has bank conflicts), then written so that
+            // 8 lanes cover one row's segment.
+            constexpr int kPasses = (kKind == 0) ? 1 : 2;
             float amax = 0.0f;
-            if (kKind == 0) {
-                // 128 outputs per row, in 4 chunks of 32; two chunks fill one 128-byte staging segment
 #pragma unroll 1
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t g[32], u[32];
-                    tmem_ld_32x32(t_addr + c * 32, g);
-                    tmem_ld_32x32(t_addr + 128 + c * 32, u);
-                    tmem_ld_wait();
+            for (int pass = 0; pass < kPasses; ++pass) {
+                const int seg_idx = half * kPasses + pass;      // 128-byte segment of this row within the tile
+#pragma unroll
+                for (int sub = 0; sub < 2; ++sub) {
+                    const int c = seg_idx * 2 + sub;             // 32-column chunk of outputs
                     uint32_t packed[16];
+                    if (kKind == 0) {
+                        uint32_t g[32], u[32];
+                        tmem_ld_32x32(t_addr + c * 32, g);
+                        tmem_ld_32x32(t_addr + 128 + c * 32, u);
+                        tmem_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < 32; j += 2) {
-                        float o[2];
+                        for (int j = 0; j < 32; j += 2) {
+                            float o[2];
 #pragma unroll
-                        for (int h = 0; h < 2; ++h) {
-                            float gv = __uint_as_float(g[j + h]) * (row_scale * sc[c * 32 + j + h]);
-                            float uv = __uint_as_float(u[j + h]) * (row_scale * sc[128 + c * 32 + j + h]);
-                            gv = fminf(fmaxf(gv, -p.clamp), p.clamp);
-                            uv = fminf(fmaxf(uv, -p.clamp), p.clamp);
-                            o[h] = silu_f(gv) * uv * route_w;
-                        }
-                        const uint32_t pk = pack_bf16x2(o[0], o[1]);
-                        packed[j / 2] = pk;
-                        amax = fmaxf(amax, fmaxf(fabsf(__uint_as_float(pk << 16)), fabsf(__uint_as_float(pk & 0xffff0000u))));
-                    }
-                    uint4* dst = reinterpret_cast<uint4*>(my_staging + lane * kStagingRowBytes + (c & 1) * 64);
-#pragma unroll
-                    for (int v = 0; v < 4; ++v) dst[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
-                    if (c & 1) {
-                        __syncwarp();
-                        // coalesced flush: 8 lanes cover one row's 128-byte segment
-#pragma unroll
-                        for (int it = 0; it < 8; ++it) {
-                            const int r = it * 4 + (lane >> 3), seg = lane & 7;
-                            if (q * 32 + r < valid) {
-                                const uint4 v = *reinterpret_cast<const uint4*>(my_staging + r * kStagingRowBytes + seg * 16);
-                                uint8_t* o = reinterpret_cast<uint8_t*>(p.act_bf16) +
-                                             (static_cast<int64_t>(mb * kBlockM + q * 32 + r) * p.n_out + nb * 128 + (c >> 1) * 64) * 2 + seg * 16;
-                                *reinterpret_cast<uint4*>(o) = v;
+                            for (int h = 0; h < 2; ++h) {
+                                float gv = __uint_as_float(g[j + h]) * (row_scale * sc[c * 32 + j + h]);
+                                float uv = __uint_as_float(u[j + h]) * (row_scale * sc[128 + c * 32 + j + h]);
+                                if (do_clamp) {
+                                    gv = fminf(fmaxf(gv, -p.clamp), p.clamp);
+                                    uv = fminf(fmaxf(uv, -p.clamp), p.clamp);
+                                }
+                                o[h] = silu_f(gv) * uv * route_w;
                             }
+                            const uint32_t pk = pack_bf16x2(o[0], o[1]);
+                            packed[j / 2] = pk;
+                            amax = fmaxf(amax, fmaxf(fabsf(__uint_as_float(pk << 16)), fabsf(__uint_as_float(pk & 0xffff0000u))));
                         }
-                        __syncwarp();
+                    } else {
+                        uint32_t a[32];
+                        tmem_ld_32x32(t_addr + c * 32, a);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 32; j += 2) {
+                            const float o0 = __uint_as_float(a[j]) * (row_scale * sc[c * 32 + j]);
+                            const float o1 = __uint_as_float(a[j + 1]) * (row_scale * sc[c * 32 + j + 1]);
+                            packed[j / 2] = pack_bf16x2(o0, o1);
+                        }
+                    }
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) {
+                        const int piece = (sub * 4 + v) ^ (lane & 7);
+                        *reinterpret_cast<uint4*>(my_staging + lane * 128 + piece * 16) =
+                            make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
                     }
                 }
-                if (row_ok) atomicMax(p.row_amax + row, __float_as_uint(amax));
-            } else {
-#pragma unroll 1
-                for (int c = 0; c < 8; ++c) {
-                    uint32_t a[32];
-                    tmem_ld_32x32(t_addr + c * 32, a);
-                    tmem_ld_wait();
-                    uint32_t packed[16];
+                __syncwarp();
+                const int col0 = (kKind == 0 ? nb * 128 : nb * kBlockN) + seg_idx * 64;   // first output column of the segment
 #pragma unroll
-                    for (int j = 0; j < 32; j += 2) {
-                        const float o0 = __uint_as_float(a[j]) * (row_scale * sc[c * 32 + j]);
-                        const float o1 = __uint_as_float(a[j + 1]) * (row_scale * sc[c * 32 + j + 1]);
-                        packed[j / 2] = pack_bf16x2(o0, o1);
-                    }
-                    uint4* dst = reinterpret_cast<uint4*>(my_staging + lane * kStagingRowBytes + (c & 1) * 64);
-#pragma unroll
-                    for (int v = 0; v < 4; ++v) dst[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
-                    if (c & 1) {
-                        __syncwarp();
-                        const int col0 = nb * kBlockN + (c >> 1) * 64;     // first output column of this segment
-#pragma unroll
-                        for (int it = 0; it < 8; ++it) {
-                            const int r = it * 4 + (lane >> 3), seg = lane & 7;
-                            const uint64_t rp = __shfl_sync(0xffffffffu, reinterpret_cast<uint64_t>(out_ptr), r);
-                            if (rp != 0 && col0 < p.n_out) {
-                                const uint4 v = *reinterpret_cast<const uint4*>(my_staging + r * kStagingRowBytes + seg * 16);
-                                *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(rp) + static_cast<int64_t>(col0) * 2 + seg * 16) = v;
-                            }
+                for (int it = 0; it < 8; ++it) {
+                    const int r = it * 4 + (lane >> 3), piece = lane & 7;
+                    const uint4 v = *reinterpret_cast<const uint4*>(my_staging + r * 128 + ((piece ^ (r & 7)) * 16));
+                    if (kKind == 0) {
+                        if (q * 32 + r < valid) {
+                            uint8_t* o = reinterpret_cast<uint8_t*>(p.act_bf16) +
+                                         (static_cast<int64_t>(mb * kBlockM + q * 32 + r) * p.n_out + col0) * 2 + piece * 16;
+                            *reinterpret_cast<uint4*>(o) = v;
                         }
-                        __syncwarp();
+                    } else {
+                        const uint64_t rp = __shfl_sync(0xffffffffu, reinterpret_cast<uint64_t>(out_ptr), r);
+                        if (rp != 0 && col0 < p.n_out)
+                            *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(rp) + static_cast<int64_t>(col0) * 2 + piece * 16) = v;
                     }
                 }
+                __syncwarp();
             }
+            if (kKind == 0 && row_ok) atomicMax(p.row_amax + row, __float_as_uint(amax));
             // accumulator buffer may be overwritten by the MMA warp
             tc_fence_before();
             __syncwarp();

@@ -349,7 +349,7 @@ int mm_fp8_w8a8_mega_moe(void* y, const void* w1, const float* s1, const void* w
     MM_STAGE(MM_STAGE_ROUTE_EXCHANGE);
     mm::route_plan_kernel<<<1, 1024, 0, stream>>>(rp);
     MM_STAGE(MM_STAGE_ROUTE_PLAN);
-    mm::dispatch_kernel<<<route_blocks, MM_ROUTE_CHUNK, 0, stream>>>(rp);
+    mm::dispatch_kernel<<<route_blocks, mm::MM_DISPATCH_THREADS, 0, stream>>>(rp);
     MM_STAGE(MM_STAGE_DISPATCH);
     if (R > 1) {
         mm::rank_barrier_kernel<<<1, 32, 0, stream>>>(rp, MM_BAR_DISPATCH);
@@ -357,7 +357,7 @@ int mm_fp8_w8a8_mega_moe(void* y, const void* w1, const float* s1, const void* w
     }
     mm::grouped_gemm_kernel<0><<<sms, mm::kGemmThreads, mm::kGemmSmemBytes, stream>>>(tm_pool, tm_w1, g1);
     MM_STAGE(MM_STAGE_GEMM1);
-    mm::requant_kernel<<<sms * 8, 256, 0, stream>>>(g1.act_bf16, I, g1.plan, g1.mblock_valid, g1.row_amax,
+    mm::requant_kernel<<<sms * 4, 256, 0, stream>>>(g1.act_bf16, I, g1.plan, g1.mblock_valid, g1.row_amax,
                                                    reinterpret_cast<float*>(sc + rp.cl.act_scale), sc + rp.cl.act_fp8);
     MM_STAGE(MM_STAGE_REQUANT);
     mm::grouped_gemm_kernel<1><<<sms, mm::kGemmThreads, mm::kGemmSmemBytes, stream>>>(tm_act, tm_w2, g2);

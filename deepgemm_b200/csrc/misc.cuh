@@ -57,42 +57,61 @@ __global__ void __launch_bounds__(256) quant_per_token_kernel(const __nv_bfloat1
 // Activation requantisation after GEMM1 (deep_gemm/include/deep_gemm/impls/mega_moe_dcu_tiles.cuh:672-733):
 //   s2 = max(amax / 448, 1e-4) ; aq = e4m3(a * (1 / s2)).  The row amax was accumulated by the GEMM1 epilogue
 // (atomicMax on the bit pattern); it is reset here so the next call starts from zero.
-// One warp per pool row; padding rows of an m-block are skipped.
+// One block per 128-row m-block (grid-stride): the block reads the m-block's valid-row count and its 128 row amax
+// values with one coalesced load, then each warp streams two rows at a time (16 independent 16-byte loads per lane).
 __global__ void __launch_bounds__(256) requant_kernel(const __nv_bfloat16* __restrict__ act, int inter,
                                                      const int* __restrict__ plan, const int* __restrict__ mblock_valid,
                                                      unsigned int* __restrict__ row_amax, float* __restrict__ act_scale,
                                                      uint8_t* __restrict__ act_q) {
-    const int lane = threadIdx.x & 31;
-    const int64_t warp = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-    const int64_t nwarps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
-    const int64_t rows = plan[1];
+    __shared__ float s_inv[MM_BLOCK_M];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int num_mblocks = plan[0];
     const int vecs = inter / 8;
-    for (int64_t r = warp; r < rows; r += nwarps) {
-        if ((r & (MM_BLOCK_M - 1)) >= mblock_valid[r / MM_BLOCK_M]) continue;
-        const float amax = __uint_as_float(row_amax[r]);
-        __syncwarp();
-        if (lane == 0) row_amax[r] = 0u;
-        const float s = fmaxf(__fdiv_rn(amax, 448.0f), 1.0e-4f);
-        const float inv = __fdiv_rn(1.0f, s);
-        if (lane == 0) act_scale[r] = s;
-        const uint4* src = reinterpret_cast<const uint4*>(act + r * inter);
-        uint2* dst = reinterpret_cast<uint2*>(act_q + r * inter);
-        for (int v0 = 0; v0 < vecs; v0 += 32 * 8) {     // eight independent 16-byte loads in flight per lane
-            uint4 buf[8];
+    for (int mb = blockIdx.x; mb < num_mblocks; mb += gridDim.x) {
+        const int valid = mblock_valid[mb];
+        __syncthreads();
+        if (threadIdx.x < MM_BLOCK_M && static_cast<int>(threadIdx.x) < valid) {
+            const int64_t r = static_cast<int64_t>(mb) * MM_BLOCK_M + threadIdx.x;
+            const float amax = __uint_as_float(row_amax[r]);
+            row_amax[r] = 0u;
+            const float s = fmaxf(__fdiv_rn(amax, 448.0f), 1.0e-4f);
+            act_scale[r] = s;
+            s_inv[threadIdx.x] = __fdiv_rn(1.0f, s);
+        }
+        __syncthreads();
+        for (int r0 = warp * 2; r0 < valid; r0 += 16) {
+            uint4 buf[2][8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int v = v0 + i * 32 + lane;
-                if (v < vecs) buf[i] = src[v];
+            for (int k = 0; k < 2; ++k) {
+                const int64_t r = static_cast<int64_t>(mb) * MM_BLOCK_M + r0 + k;
+                const uint4* src = reinterpret_cast<const uint4*>(act + r * inter);
+                if (r0 + k < valid) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int v = i * 32 + lane;
+                        if (v < vecs) buf[k][i] = src[v];
+                    }
+                }
             }
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int v = v0 + i * 32 + lane;
-                if (v < vecs) {
-                    const uint4 d = buf[i];
-                    uint2 o;
-                    o.x = pack4_e4m3(bf16_lo(d.x) * inv, bf16_hi(d.x) * inv, bf16_lo(d.y) * inv, bf16_hi(d.y) * inv);
-                    o.y = pack4_e4m3(bf16_lo(d.z) * inv, bf16_hi(d.z) * inv, bf16_lo(d.w) * inv, bf16_hi(d.w) * inv);
-                    dst[v] = o;
+            for (int k = 0; k < 2; ++k) {
+                if (r0 + k >= valid) continue;
+                const int64_t r = static_cast<int64_t>(mb) * MM_BLOCK_M + r0 + k;
+                const float inv = s_inv[r0 + k];
+                const uint4* src = reinterpret_cast<const uint4*>(act + r * inter);
+                uint2* dst = reinterpret_cast<uint2*>(act_q + r * inter);
+                for (int v0 = 0; v0 < vecs; v0 += 256) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int v = v0 + i * 32 + lane;
+                        if (v < vecs) {
+                            const uint4 d = (v0 == 0) ? buf[k][i] : src[v];   // rows longer than 2048 read the rest directly
+                            uint2 o;
+                            o.x = pack4_e4m3(bf16_lo(d.x) * inv, bf16_hi(d.x) * inv, bf16_lo(d.y) * inv, bf16_hi(d.y) * inv);
+                            o.y = pack4_e4m3(bf16_lo(d.z) * inv, bf16_hi(d.z) * inv, bf16_lo(d.w) * inv, bf16_hi(d.w) * inv);
+                            dst[v] = o;
+                        }
+                    }
                 }
             }
         }
@@ -102,7 +121,7 @@ __global__ void __launch_bounds__(256) requant_kernel(const __nv_bfloat16* __res
 // Top-k combine (deep_gemm/include/deep_gemm/impls/mega_moe_dcu.cuh:706-760):
 //   y[t, :] = bf16( sum_{s=0..K-1} f32(combine[s][t][:]) ) in slot order; slots of invalid routes contribute zero.
 // The reference zeroes those slots during its route scan; here they are skipped using the same validity rule.
-__global__ void __launch_bounds__(256) combine_reduce_kernel(const uint8_t* __restrict__ sym, MmSymLayout sl, int E, int T, int K, int H,
+__global__ void __launch_bounds__(256, 4) combine_reduce_kernel(const uint8_t* __restrict__ sym, MmSymLayout sl, int E, int T, int K, int H,
                                                             int num_tokens, const int* __restrict__ runtime_num_tokens,
                                                             __nv_bfloat16* __restrict__ y) {
     int n = runtime_num_tokens ? *runtime_num_tokens : num_tokens;
@@ -116,11 +135,11 @@ __global__ void __launch_bounds__(256) combine_reduce_kernel(const uint8_t* __re
          i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
         const int t = static_cast<int>(i / vecs), v = static_cast<int>(i - static_cast<int64_t>(t) * vecs);
         float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        for (int s0 = 0; s0 < K; s0 += 8) {             // up to eight slots' loads in flight, summed in slot order
-            uint4 buf[8];
-            bool ok[8];
+        for (int s0 = 0; s0 < K; s0 += 6) {             // up to six slots' loads in flight, summed in slot order
+            uint4 buf[6];
+            bool ok[6];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
+            for (int j = 0; j < 6; ++j) {
                 const int s = s0 + j;
                 ok[j] = false;
                 if (s < K) {
@@ -131,7 +150,7 @@ __global__ void __launch_bounds__(256) combine_reduce_kernel(const uint8_t* __re
                 }
             }
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
+            for (int j = 0; j < 6; ++j) {
                 if (!ok[j]) continue;
                 const uint4 d = buf[j];
                 acc[0] += bf16_lo(d.x); acc[1] += bf16_hi(d.x); acc[2] += bf16_lo(d.y); acc[3] += bf16_hi(d.y);

@@ -194,41 +194,45 @@ __global__ void __launch_bounds__(1024) route_plan_kernel(RouteParams p) {
 }
 
 // ---- 4. slot assignment + push -----------------------------------------------------------------------------------
-// grid = route_blocks, block = MM_ROUTE_CHUNK.  Thread i owns route b*CHUNK+i; its pool row on the owner is
+// grid = route_blocks, block = MM_DISPATCH_THREADS.  Thread i < CHUNK owns route b*CHUNK+i; its pool row on the owner is
 //   dest_base[e] + (rows of earlier blocks for e) + (earlier routes of this block with the same e).
-// Then each warp copies its 32 routes' rows (H bytes of fp8 + 16 bytes of metadata) to the owners' pools.
-__global__ void __launch_bounds__(MM_ROUTE_CHUNK) dispatch_kernel(RouteParams p) {
+// Then all warps of the block copy the chunk's rows (H bytes of fp8 + 16 bytes of metadata) to the owners' pools.
+constexpr int MM_DISPATCH_THREADS = 1024;
+__global__ void __launch_bounds__(MM_DISPATCH_THREADS) dispatch_kernel(RouteParams p) {
     __shared__ int s_e[MM_ROUTE_CHUNK];
     __shared__ int s_row[MM_ROUTE_CHUNK];
     const int n_routes = route_num_tokens(p) * p.K;
     const int route = blockIdx.x * MM_ROUTE_CHUNK + threadIdx.x;
+    const bool owner_thread = threadIdx.x < MM_ROUTE_CHUNK;
     int e = -1;
     float w = 0.0f;
-    if (route < n_routes) {
+    if (owner_thread && route < n_routes) {
         const int64_t e64 = reinterpret_cast<const int64_t*>(p.sym + p.sl.topk_idx)[route];
         w = reinterpret_cast<const float*>(p.sym + p.sl.topk_weights)[route];
         if (e64 >= 0 && e64 < p.E && w != 0.0f) e = static_cast<int>(e64);
     }
-    s_e[threadIdx.x] = e;
+    if (owner_thread) s_e[threadIdx.x] = e;
     __syncthreads();
     int row = -1;
-    if (e >= 0) {
+    if (owner_thread && e >= 0) {
         int within = 0;
         for (int j = 0; j < static_cast<int>(threadIdx.x); ++j) within += (s_e[j] == e);
         const int* bc = reinterpret_cast<const int*>(p.scratch + p.cl.block_counts) + static_cast<int64_t>(blockIdx.x) * p.E;
         row = reinterpret_cast<const int*>(p.scratch + p.cl.dest_base)[e] + bc[e] + within;
         if (row >= p.sl.pool_rows) row = -1;   // cannot happen with worst-case sizing; never write out of bounds
     }
-    s_row[threadIdx.x] = row;
-    if (route < n_routes) reinterpret_cast<int*>(p.scratch + p.cl.dest_row)[route] = row;
+    if (owner_thread) {
+        s_row[threadIdx.x] = row;
+        if (route < n_routes) reinterpret_cast<int*>(p.scratch + p.cl.dest_row)[route] = row;
+    }
     __syncthreads();
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint8_t* x = p.sym + p.sl.x;
     const float* x_sf = reinterpret_cast<const float*>(p.sym + p.sl.x_sf);
     const float* tw = reinterpret_cast<const float*>(p.sym + p.sl.topk_weights);
-    for (int i = 0; i < 32; ++i) {
-        const int li = warp * 32 + i;
+    constexpr int kWarps = MM_DISPATCH_THREADS / 32;
+    for (int li = warp; li < MM_ROUTE_CHUNK; li += kWarps) {
         const int r_row = s_row[li];
         if (r_row < 0) continue;
         const int r_e = s_e[li];

@@ -29,9 +29,10 @@ import torch  # noqa: E402
 E, K, H, I = 256, 6, 4096, 2048
 METRIC, UNIT = "moe_layer_tokens_per_s", "tokens/s"
 FLOP_PER_ROW = 2 * 3 * H * I                     # 50.33 MFLOP per routed row (GEMM1 33.55 + GEMM2 16.78)
-# DRAM read+write bytes of one GEMM1 launch at the N=1 workload, from the ncu capture summarised in
-# profiles/gemm1_dsv4_ep1.md (a 32-expert case scaled by the experts processed); None until captured
-GEMM1_DRAM_TRAFFIC_BYTES = None
+# DRAM read+write bytes of one GEMM1 launch per expert processed, from the ncu capture summarised in
+# profiles/grouped_gemm_dsv4_32experts_512tok.md (566.9 MB for 32 experts with 96 rows each; traffic grows with the
+# experts processed, so a launch over n experts moves n times this)
+GEMM1_DRAM_TRAFFIC_BYTES_PER_EXPERT = 566.9e6 / 32
 
 
 def measured_peaks():
@@ -316,7 +317,7 @@ def main():
         "gpu_launches": launches,
         "clocks": clocks,
         "roofline": {"kernel": "grouped_gemm_kernel<0> (GEMM1 + SwiGLU)", "bound": "hbm", "achieved": achieved, "peak": hbm_peak,
-                     "unit": "GB/s", "frac": achieved / hbm_peak, "peak_kind": f"of {peak_kind}", "traffic": GEMM1_DRAM_TRAFFIC_BYTES,
+                     "unit": "GB/s", "frac": achieved / hbm_peak, "peak_kind": f"of {peak_kind}", "traffic": GEMM1_DRAM_TRAFFIC_BYTES_PER_EXPERT * touched,
                      "algorithmic_bytes": gemm1_bytes, "ms": gemm1_ms},
         "stage_ms": {k_: round(v, 4) for k_, v in acc.items()},
     }

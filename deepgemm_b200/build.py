@@ -16,7 +16,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_NAME = "libmegamoe_b200.so"
 LIB_PATH = os.path.join(HERE, LIB_NAME)
-SOURCES = ["abi.cu"]
+SOURCES = ["abi.cu", "noalloc.cu"]
 HEADERS = ["layout.h", "ptx.cuh", "route.cuh", "gemm.cuh", "misc.cuh", "fused.cuh", "noalloc.cuh",
            os.path.join("..", "..", "include", "megamoe_b200.h")]
 

@@ -168,6 +168,9 @@ int stage_end(int id, cudaStream_t stream) {
 
 }  // namespace
 
+// lets the other translation units of the library report through mm_last_error
+void mm_detail_set_error(const char* msg) { snprintf(g_err, sizeof(g_err), "%s", msg); }
+
 extern "C" {
 
 const char* mm_last_error(void) { return g_err; }

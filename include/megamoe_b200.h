@@ -105,6 +105,27 @@ int mm_build_config(char* json, int capacity);
 /* Number of kernels the library has launched in this process (all entry points). */
 int64_t mm_launch_count(void);
 
+/* Size of the work area built into the library for mm_fp8_w8a8_mega_moe_static (bytes, per GPU). */
+#define MM_STATIC_WORK_BYTES (64u << 20)
+
+/* The single-rank layer WITHOUT caller-provided work buffers, for hosts that are not allowed to allocate device
+ * memory (a serving process whose memory arena owns all of HBM, a code path where cudaMalloc's device-wide
+ * synchronisation is unacceptable, a plugin that may only touch the tensors it is handed).  It has no counterpart in
+ * the reference, which always allocates its symmetric buffer and route scratch itself (megamoe/__init__.py:172-177).
+ * The symmetric and scratch regions live in a device array of MM_STATIC_WORK_BYTES that is part of the library image:
+ * every GPU that loads the library holds it until the process exits.  Shapes whose regions do not fit (see
+ * mm_symm_buffer_layout / mm_scratch_layout with R = 1 and T = num_tokens rounded up to 384) are rejected with an error.
+ * x_fp8 [num_tokens,H], x_sf [num_tokens], topk_idx int64 [num_tokens,K], topk_weights f32 [num_tokens,K] and y bf16
+ * [num_tokens,H] are device pointers; weights/scales/stats/clamp as for mm_fp8_w8a8_mega_moe, num_experts = all experts.
+ * No cudaMalloc, cudaFree or other allocating call is made.  The first call on each device looks up the address of
+ * the built-in area (cudaGetSymbolAddress); make that first call outside any stream capture.  All calls on a device
+ * share the area and it keeps the previous call's contents, so each call first clears the words that must start at
+ * zero; two calls that overlap on the GPU (different streams) race -- serialise them. */
+int mm_fp8_w8a8_mega_moe_static(void* y, const void* x_fp8, const float* x_sf, const int64_t* topk_idx,
+                                const float* topk_weights, const void* w1, const float* s1, const void* w2, const float* s2,
+                                int* stats, int num_tokens, int num_experts, int K, int H, int I, float activation_clamp,
+                                void* stream);
+
 /* Per-stage device timing of the layer call (the reference's test prints per-kernel times with a profiler,
  * tests/test_mega_moe_dcu.py:794-834; here CUDA events are recorded on the caller's stream around every launch).
  * mm_set_stage_timing(1) turns recording on for later calls; mm_get_stage_times waits for the last timed call and

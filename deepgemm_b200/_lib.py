@@ -47,7 +47,7 @@ _SIGNATURES = {
     "mm_get_stage_times": (c_int, [POINTER(c_float), c_int]),
 }
 STAGE_NAMES = ["route_count", "route_exchange", "route_plan", "dispatch", "barrier_dispatch", "gemm1", "requant", "gemm2",
-               "barrier_combine", "reduce"]
+               "barrier_combine", "reduce", "fused"]
 EXPORTED_SYMBOLS = tuple(_SIGNATURES)
 
 _lib = None

@@ -11,6 +11,7 @@
 #include <vector>
 
 #include "../../include/megamoe_b200.h"
+#include "fused.cuh"
 #include "gemm.cuh"
 #include "layout.h"
 #include "misc.cuh"
@@ -129,6 +130,7 @@ int ensure_gemm_attrs() {
     if (dev < 64 && done[dev]) return 0;
     MM_CUDA(cudaFuncSetAttribute(mm::grouped_gemm_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, mm::kGemmSmemBytes));
     MM_CUDA(cudaFuncSetAttribute(mm::grouped_gemm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, mm::kGemmSmemBytes));
+    MM_CUDA(cudaFuncSetAttribute(mm::mega_moe_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, mm::kGemmSmemBytes));
     if (dev < 64) done[dev] = true;
     return 0;
 }
@@ -342,7 +344,29 @@ int mm_fp8_w8a8_mega_moe(void* y, const void* w1, const float* s1, const void* w
     g1.kdim = H; g1.n_blocks = I / 128; g1.n_out = I; g1.w_rows_per_expert = 2 * I; g1.w_scale = s1;
     g2.kdim = I; g2.n_blocks = (H + mm::kBlockN - 1) / mm::kBlockN; g2.n_out = H; g2.w_rows_per_expert = H; g2.w_scale = s2;
 
-    if (mode == MM_MODE_FUSED) return fail(2, "the fused variant is not available in this build");
+    if (mode == MM_MODE_FUSED) {
+        MM_REQUIRE(tokens_bound * K <= mm::kFusedMaxRoutes,
+                   "the fused variant holds at most %d routes (tokens x top-k) per rank; use the staged variant", mm::kFusedMaxRoutes);
+        mm::FusedParams fp;
+        memset(&fp, 0, sizeof(fp));
+        fp.rp = rp;
+        fp.g1 = g1;
+        fp.g2 = g2;
+        fp.y = static_cast<__nv_bfloat16*>(y);
+        fp.l1_done = reinterpret_cast<int*>(sc + rp.cl.l1_done);
+        fp.l2_ready = reinterpret_cast<int*>(sc + rp.cl.l2_ready);
+        fp.grid_sync = reinterpret_cast<int*>(sc + rp.cl.grid_sync);
+        fp.act_fp8 = sc + rp.cl.act_fp8;
+        fp.act_scale_w = reinterpret_cast<float*>(sc + rp.cl.act_scale);
+        if (int rc = stage_begin(stream)) return rc;
+        void* args[] = {&tm_pool, &tm_w1, &tm_act, &tm_w2, &fp};
+        // cooperative launch: all CTAs must be resident because they wait on one another
+        MM_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(mm::mega_moe_fused_kernel), dim3(sms), dim3(mm::kFusedThreads),
+                                            args, mm::kGemmSmemBytes, stream));
+        MM_LAUNCHED();
+        if (int rc = stage_end(MM_STAGE_FUSED, stream)) return rc;
+        return 0;
+    }
 
     if (int rc = stage_begin(stream)) return rc;
 #define MM_STAGE(id) do { MM_LAUNCHED(); if (int rc_ = stage_end(id, stream)) return rc_; } while (0)

@@ -66,6 +66,89 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// Epilogue arithmetic of one output tile for one epilogue warp: read this warp's share of the accumulator from TMEM,
+// apply the scales (kind 0: SwiGLU x route weight and the row amax), and write 128-byte row segments.
+//   q = TMEM lane quarter of the warp, half = which half of the tile's columns it handles, acc = accumulator buffer.
+template <int kKind>
+__device__ __forceinline__ void epilogue_math(const GemmParams& p, uint32_t tmem_base, const float* sc, uint8_t* my_staging,
+                                              int lane, int q, int half, int acc, int mb, int nb, int valid, int row, bool row_ok,
+                                              float row_scale, float route_w, uint8_t* out_ptr, bool do_clamp) {
+    const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * kBlockN;
+    // Each pass handles one 128-byte output segment (64 bf16) per row: two 32-column chunks, staged in shared
+    // memory (16-byte pieces XOR-swizzled by row so neither phase has bank conflicts), then written so that
+    // 8 lanes cover one row's segment.
+    constexpr int kPasses = (kKind == 0) ? 1 : 2;
+    float amax = 0.0f;
+#pragma unroll 1
+    for (int pass = 0; pass < kPasses; ++pass) {
+        const int seg_idx = half * kPasses + pass;      // 128-byte segment of this row within the tile
+#pragma unroll
+        for (int sub = 0; sub < 2; ++sub) {
+            const int c = seg_idx * 2 + sub;             // 32-column chunk of outputs
+            uint32_t packed[16];
+            if (kKind == 0) {
+                uint32_t g[32], u[32];
+                tmem_ld_32x32(t_addr + c * 32, g);
+                tmem_ld_32x32(t_addr + 128 + c * 32, u);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 32; j += 2) {
+                    float o[2];
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        float gv = __uint_as_float(g[j + h]) * (row_scale * sc[c * 32 + j + h]);
+                        float uv = __uint_as_float(u[j + h]) * (row_scale * sc[128 + c * 32 + j + h]);
+                        if (do_clamp) {
+                            gv = fminf(fmaxf(gv, -p.clamp), p.clamp);
+                            uv = fminf(fmaxf(uv, -p.clamp), p.clamp);
+                        }
+                        o[h] = silu_f(gv) * uv * route_w;
+                    }
+                    const uint32_t pk = pack_bf16x2(o[0], o[1]);
+                    packed[j / 2] = pk;
+                    amax = fmaxf(amax, fmaxf(fabsf(__uint_as_float(pk << 16)), fabsf(__uint_as_float(pk & 0xffff0000u))));
+                }
+            } else {
+                uint32_t a[32];
+                tmem_ld_32x32(t_addr + c * 32, a);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 32; j += 2) {
+                    const float o0 = __uint_as_float(a[j]) * (row_scale * sc[c * 32 + j]);
+                    const float o1 = __uint_as_float(a[j + 1]) * (row_scale * sc[c * 32 + j + 1]);
+                    packed[j / 2] = pack_bf16x2(o0, o1);
+                }
+            }
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+                const int piece = (sub * 4 + v) ^ (lane & 7);
+                *reinterpret_cast<uint4*>(my_staging + lane * 128 + piece * 16) =
+                    make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+            }
+        }
+        __syncwarp();
+        const int col0 = (kKind == 0 ? nb * 128 : nb * kBlockN) + seg_idx * 64;   // first output column of the segment
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+            const int r = it * 4 + (lane >> 3), piece = lane & 7;
+            const uint4 v = *reinterpret_cast<const uint4*>(my_staging + r * 128 + ((piece ^ (r & 7)) * 16));
+            if (kKind == 0) {
+                if (q * 32 + r < valid) {
+                    uint8_t* o = reinterpret_cast<uint8_t*>(p.act_bf16) +
+                                 (static_cast<int64_t>(mb * kBlockM + q * 32 + r) * p.n_out + col0) * 2 + piece * 16;
+                    *reinterpret_cast<uint4*>(o) = v;
+                }
+            } else {
+                const uint64_t rp = __shfl_sync(0xffffffffu, reinterpret_cast<uint64_t>(out_ptr), r);
+                if (rp != 0 && col0 < p.n_out)
+                    *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(rp) + static_cast<int64_t>(col0) * 2 + piece * 16) = v;
+            }
+        }
+        __syncwarp();
+    }
+    if (kKind == 0 && row_ok) atomicMax(p.row_amax + row, __float_as_uint(amax));
+}
+
 template <int kKind>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, GemmParams p) {
@@ -214,80 +297,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             }
             if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.timeout_ns)) { alive = false; break; }
             tc_fence_after();
-            const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * kBlockN;
-            // Each pass handles one 128-byte output segment (64 bf16) per row: two 32-column chunks, staged in shared
-            // memory (16-byte pieces XOR-swizzled by row so neither phase has bank conflicts), then written so that
-            // 8 lanes cover one row's segment.
-            constexpr int kPasses = (kKind == 0) ? 1 : 2;
-            float amax = 0.0f;
-#pragma unroll 1
-            for (int pass = 0; pass < kPasses; ++pass) {
-                const int seg_idx = half * kPasses + pass;      // 128-byte segment of this row within the tile
-#pragma unroll
-                for (int sub = 0; sub < 2; ++sub) {
-                    const int c = seg_idx * 2 + sub;             // 32-column chunk of outputs
-                    uint32_t packed[16];
-                    if (kKind == 0) {
-                        uint32_t g[32], u[32];
-                        tmem_ld_32x32(t_addr + c * 32, g);
-                        tmem_ld_32x32(t_addr + 128 + c * 32, u);
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int j = 0; j < 32; j += 2) {
-                            float o[2];
-#pragma unroll
-                            for (int h = 0; h < 2; ++h) {
-                                float gv = __uint_as_float(g[j + h]) * (row_scale * sc[c * 32 + j + h]);
-                                float uv = __uint_as_float(u[j + h]) * (row_scale * sc[128 + c * 32 + j + h]);
-                                if (do_clamp) {
-                                    gv = fminf(fmaxf(gv, -p.clamp), p.clamp);
-                                    uv = fminf(fmaxf(uv, -p.clamp), p.clamp);
-                                }
-                                o[h] = silu_f(gv) * uv * route_w;
-                            }
-                            const uint32_t pk = pack_bf16x2(o[0], o[1]);
-                            packed[j / 2] = pk;
-                            amax = fmaxf(amax, fmaxf(fabsf(__uint_as_float(pk << 16)), fabsf(__uint_as_float(pk & 0xffff0000u))));
-                        }
-                    } else {
-                        uint32_t a[32];
-                        tmem_ld_32x32(t_addr + c * 32, a);
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int j = 0; j < 32; j += 2) {
-                            const float o0 = __uint_as_float(a[j]) * (row_scale * sc[c * 32 + j]);
-                            const float o1 = __uint_as_float(a[j + 1]) * (row_scale * sc[c * 32 + j + 1]);
-                            packed[j / 2] = pack_bf16x2(o0, o1);
-                        }
-                    }
-#pragma unroll
-                    for (int v = 0; v < 4; ++v) {
-                        const int piece = (sub * 4 + v) ^ (lane & 7);
-                        *reinterpret_cast<uint4*>(my_staging + lane * 128 + piece * 16) =
-                            make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
-                    }
-                }
-                __syncwarp();
-                const int col0 = (kKind == 0 ? nb * 128 : nb * kBlockN) + seg_idx * 64;   // first output column of the segment
-#pragma unroll
-                for (int it = 0; it < 8; ++it) {
-                    const int r = it * 4 + (lane >> 3), piece = lane & 7;
-                    const uint4 v = *reinterpret_cast<const uint4*>(my_staging + r * 128 + ((piece ^ (r & 7)) * 16));
-                    if (kKind == 0) {
-                        if (q * 32 + r < valid) {
-                            uint8_t* o = reinterpret_cast<uint8_t*>(p.act_bf16) +
-                                         (static_cast<int64_t>(mb * kBlockM + q * 32 + r) * p.n_out + col0) * 2 + piece * 16;
-                            *reinterpret_cast<uint4*>(o) = v;
-                        }
-                    } else {
-                        const uint64_t rp = __shfl_sync(0xffffffffu, reinterpret_cast<uint64_t>(out_ptr), r);
-                        if (rp != 0 && col0 < p.n_out)
-                            *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(rp) + static_cast<int64_t>(col0) * 2 + piece * 16) = v;
-                    }
-                }
-                __syncwarp();
-            }
-            if (kKind == 0 && row_ok) atomicMax(p.row_amax + row, __float_as_uint(amax));
+            epilogue_math<kKind>(p, tmem_base, sc, my_staging, lane, q, half, acc, mb, nb, valid, row, row_ok, row_scale, route_w,
+                                 out_ptr, do_clamp);
             // accumulator buffer may be overwritten by the MMA warp
             tc_fence_before();
             __syncwarp();

@@ -35,8 +35,10 @@ _LARGE_OPT_DEFAULT_THRESHOLD = 128
 # un-prefixed aliases of the reference's environment variables
 _ALIASES = {_LARGE_OPT_ENV: "MEGAMOE_USE_STAGED", _LARGE_OPT_THRESHOLD_ENV: "MEGAMOE_STAGED_TOKEN_THRESHOLD"}
 
-# the fused single-launch variant is selected for token counts at or below the threshold once it is built in
-_FUSED_AVAILABLE = False
+# the fused single-launch variant is selected for token counts at or below the threshold; it keeps a rank's routes in
+# shared memory, so it is limited to this many routes (tokens x top-k) per rank -- larger calls always run staged
+_FUSED_AVAILABLE = True
+_FUSED_MAX_ROUTES = 4096
 
 
 def _align(value: int, alignment: int) -> int:
@@ -450,8 +452,8 @@ def fp8_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer: SymmBuffer
         staged = _large_opt_3stage_selected(dispatch_tokens, sb._large_opt_3stage_mode, sb._large_opt_3stage_threshold)
         call_y = y
         runtime_ptr = None
-    if not _FUSED_AVAILABLE:
-        staged = True
+    if not staged and not graph_mode and int(call_y.size(0)) * sb.num_topk > _FUSED_MAX_ROUTES:
+        staged = True      # beyond the fused kernel's shared-memory routing capacity (same rule on every rank: uniform shapes)
 
     # argument checks of csrc/apis/mega_dcu.hpp:355-445
     if tuple(recipe) != (1, 1, 32):

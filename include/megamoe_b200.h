@@ -34,7 +34,8 @@ enum {
 /* stages of one staged layer call, in launch order (indices of mm_get_stage_times) */
 enum {
     MM_STAGE_ROUTE_COUNT = 0, MM_STAGE_ROUTE_EXCHANGE, MM_STAGE_ROUTE_PLAN, MM_STAGE_DISPATCH, MM_STAGE_BARRIER_DISPATCH,
-    MM_STAGE_GEMM1, MM_STAGE_REQUANT, MM_STAGE_GEMM2, MM_STAGE_BARRIER_COMBINE, MM_STAGE_REDUCE, MM_NUM_STAGES
+    MM_STAGE_GEMM1, MM_STAGE_REQUANT, MM_STAGE_GEMM2, MM_STAGE_BARRIER_COMBINE, MM_STAGE_REDUCE,
+    MM_STAGE_FUSED /* the single launch of MM_MODE_FUSED */, MM_NUM_STAGES
 };
 /* execution variants of mm_fp8_w8a8_mega_moe */
 enum { MM_MODE_STAGED = 0, MM_MODE_FUSED = 1 };

@@ -70,8 +70,9 @@ def run_oracle(case: Case, clamp=None, variant="fused", trace=False):
 
 
 def run_cuda_rank(case: Case, rank: int, group=None, clamp=None, t_max: Optional[int] = None, stats=None,
-                  marlin=False, sb=None, keep=False, quantise_on_device=True, **kwargs):
-    """Run one rank of the case on the current CUDA device through the megamoe API. Returns (y, sym_buffer|None)."""
+                  marlin=False, sb=None, keep=False, quantise_on_device=True, variant=None, **kwargs):
+    """Run one rank of the case on the current CUDA device through the megamoe API. Returns (y, sym_buffer|None).
+    variant: None = the API's token-threshold choice, "fused" / "staged" = force that kernel variant."""
     import megamoe
     dev = torch.device("cuda", torch.cuda.current_device())
     T = case.tokens[rank]
@@ -79,6 +80,8 @@ def run_cuda_rank(case: Case, rank: int, group=None, clamp=None, t_max: Optional
     own = sb is None
     if own:
         sb = megamoe.get_symm_buffer_for_mega_moe(group, case.E, t_cap, case.K, case.H, case.I)
+    if variant is not None:
+        sb._large_opt_3stage_mode = {"fused": "off", "staged": "force"}[variant]
     if quantise_on_device:
         w1 = megamoe.transform_fp8_weights_for_mega_moe(case.w1_bf16[rank].to(dev), case.w2_bf16[rank].to(dev),
                                                         layout="marlin" if marlin else "tiled")

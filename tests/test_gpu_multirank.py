@@ -37,7 +37,7 @@ def _worker(rank, world, port, cfg):
         ys, lay, tr = mc.run_oracle(case, cfg.get("clamp"), "fused", trace=True)
         stats = torch.zeros((cfg["E"] // world,), dtype=torch.int32, device="cuda")
         y, sb = mc.run_cuda_rank(case, rank, group=dist.group.WORLD, clamp=cfg.get("clamp"), keep=True,
-                                 t_max=max(max(tokens), 1), stats=stats)
+                                 t_max=max(max(tokens), 1), stats=stats, variant=cfg.get("variant"))
         f = mc.compare_stages(case, rank, sb, lay, tr, log=lambda *_: None)
         for key in ("x_q_equal", "x_s_equal", "dest_row_equal", "totals_equal", "pool_off_equal", "plan_rows_equal",
                     "pool_rows_equal", "pool_meta_equal"):
@@ -48,7 +48,7 @@ def _worker(rank, world, port, cfg):
             assert f["act_q_mismatch_frac"] < 1e-3 and f["act_scale_max_rel"] < 1e-2, (rank, f)
         mc.assert_end_to_end_close(y, ys[rank], f"rank {rank}")
         # a second call on the same buffers reproduces the first bit for bit
-        y2, _ = mc.run_cuda_rank(case, rank, group=dist.group.WORLD, clamp=cfg.get("clamp"), sb=sb)
+        y2, _ = mc.run_cuda_rank(case, rank, group=dist.group.WORLD, clamp=cfg.get("clamp"), sb=sb, variant=cfg.get("variant"))
         assert torch.equal(y.view(torch.int16), y2.view(torch.int16)), f"rank {rank}: not deterministic"
         sb.destroy()
     finally:
@@ -64,7 +64,19 @@ def _run(world, cfg):
 
 
 def test_ep2_small():
-    _run(2, dict(E=8, K=2, H=512, I=256, tokens=[128, 128], seed=20))
+    _run(2, dict(E=8, K=2, H=512, I=256, tokens=[128, 128], seed=20, variant="staged"))
+
+
+def test_ep2_small_fused_variant():
+    _run(2, dict(E=8, K=2, H=512, I=256, tokens=[128, 100], seed=20, variant="fused"))
+
+
+def test_ep2_dsv4_shaped_fused_variant():
+    _run(2, dict(E=32, K=6, H=4096, I=2048, tokens=[300, 256], seed=23, variant="fused"))
+
+
+def test_ep8_decode_shaped_fused_variant():
+    _run(8, dict(E=64, K=6, H=1024, I=512, tokens=[128, 0, 64, 128, 1, 17, 96, 128], seed=26, variant="fused"))
 
 
 def test_ep2_uneven_tokens_invalid_routes_clamp():

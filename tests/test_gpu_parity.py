@@ -119,9 +119,46 @@ def test_input_cast_bit_exact_random_and_edges():
     assert torch.equal(q.cpu().view(torch.uint8), q_ref.view(torch.uint8))
 
 
-def test_small_config_literal_bar():
+@pytest.mark.parametrize("variant", ["staged", "fused"])
+def test_small_config_literal_bar(variant):
     """256 tokens, hidden 512, intermediate 256, 8 experts, top-2, seed 0 (the CPU-runnable configuration)."""
-    _check_case(mc.make_case(1, 8, 2, 512, 256, [256], seed=0), literal_bar=True)
+    _check_case(mc.make_case(1, 8, 2, 512, 256, [256], seed=0), literal_bar=True, variant=variant)
+
+
+def test_fused_and_staged_variants_are_bitwise_identical():
+    """Both variants run the same arithmetic in the same order per row, so their outputs agree bit for bit."""
+    case = mc.make_case(1, 16, 4, 512, 256, [300], seed=14, invalid_fraction=0.1)
+    a, _ = mc.run_cuda_rank(case, 0, variant="staged", clamp=10.0)
+    b, _ = mc.run_cuda_rank(case, 0, variant="fused", clamp=10.0)
+    assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+
+
+@pytest.mark.parametrize("tokens,invalid", [(0, 0.0), (1, 0.0), (33, 0.3), (512, 0.0)])
+def test_fused_variant_edge_cases(tokens, invalid):
+    _check_case(mc.make_case(1, 8, 2, 512, 256, [tokens], seed=15, invalid_fraction=invalid), variant="fused",
+                t_max=max(tokens, 64))
+
+
+def test_fused_variant_dsv4_shaped_slice_and_reuse():
+    case = mc.make_case(1, 16, 6, 4096, 2048, [512], seed=10)
+    _check_case(case, variant="fused")
+    y, sb = mc.run_cuda_rank(case, 0, variant="fused", keep=True)
+    y2, _ = mc.run_cuda_rank(case, 0, variant="fused", sb=sb)     # counters were left clean by the first call
+    y3, _ = mc.run_cuda_rank(case, 0, variant="staged", sb=sb)    # and the two variants can alternate on one buffer
+    sb.destroy()
+    assert torch.equal(y.view(torch.int16), y2.view(torch.int16)) and torch.equal(y.view(torch.int16), y3.view(torch.int16))
+
+
+def test_fused_variant_refuses_more_routes_than_it_can_hold():
+    import megamoe
+    from deepgemm_b200 import _lib
+    case = mc.make_case(1, 8, 2, 512, 256, [16], seed=16)
+    sb = megamoe.get_symm_buffer_for_mega_moe(None, 8, 4000, 2, 512, 256)
+    l1, l2 = megamoe.transform_fp8_weights_for_mega_moe(case.w1_bf16[0].cuda(), case.w2_bf16[0].cuda())
+    y = torch.empty((4000, 512), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(_lib.MegaMoeError):          # graph mode bounds the routes by the buffer capacity: 4224 * 2 > 4096
+        megamoe.fp8_mega_moe(y, l1, l2, sb, big_fused_cuda_graph=True)
+    sb.destroy()
 
 
 @pytest.mark.parametrize("clamp", [10.0, 1.0])
@@ -231,7 +268,8 @@ def test_api_argument_errors():
     sb.destroy()
 
 
-def test_graph_bucket_mode_uses_device_side_token_count():
+@pytest.mark.parametrize("variant", ["staged", "fused"])
+def test_graph_bucket_mode_uses_device_side_token_count(variant):
     """CUDA-graph bucket semantics (README 'CUDA Graph' section of the reference; tests/test_mega_moe_dcu.py:563-715):
     the call is captured once for the bucket size and replayed with different device-side token counts."""
     import megamoe
@@ -243,11 +281,12 @@ def test_graph_bucket_mode_uses_device_side_token_count():
     sb.x[:96].copy_(xq); sb.x_sf[:96].copy_(xs)
     sb.topk_idx[:96].copy_(case.idx[0].cuda()); sb.topk_weights[:96].copy_(case.w[0].cuda())
     y = torch.zeros((96, 512), dtype=torch.bfloat16, device="cuda")
-    megamoe.fp8_mega_moe(y, l1, l2, sb, stages_fused_cuda_graph=True)   # warm-up outside capture
+    flag = {"staged": dict(stages_fused_cuda_graph=True), "fused": dict(big_fused_cuda_graph=True)}[variant]
+    megamoe.fp8_mega_moe(y, l1, l2, sb, **flag)   # warm-up outside capture
     torch.cuda.synchronize()
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.graph(graph):
-        megamoe.fp8_mega_moe(y, l1, l2, sb, stages_fused_cuda_graph=True)
+        megamoe.fp8_mega_moe(y, l1, l2, sb, **flag)
     for n in (96, 40, 0, 77):
         y.fill_(7.0)
         sb.cuda_graph_num_tokens.fill_(n)

@@ -194,6 +194,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--tokens", type=int, default=4096, help="tokens per rank")
+    ap.add_argument("--variant", default="auto", choices=["auto", "fused", "staged"],
+                    help="kernel variant: auto = the API's token threshold (fused up to 128 tokens, staged above)")
     ap.add_argument("--experts", type=int, default=E, help="total experts (reduce only for small profiler captures)")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -211,6 +213,9 @@ def main():
     e_loc = E // world
     l1, l2, x_bf16, idx, w = make_rank_data(rank, world, T, dev)
     sb = megamoe.get_symm_buffer_for_mega_moe(group, E, T, K, H, I)
+    if args.variant != "auto":
+        sb._large_opt_3stage_mode = {"fused": "off", "staged": "force"}[args.variant]
+    staged = megamoe._large_opt_3stage_selected(T, sb._large_opt_3stage_mode, sb._large_opt_3stage_threshold) or T * K > 4096
     y = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
     stream = torch.cuda.current_stream().cuda_stream
     lib = _lib.lib()
@@ -295,10 +300,18 @@ def main():
     megamoe.fp8_w8a8_mega_moe(y, l1, l2, sb, cumulative_local_expert_recv_stats=stats)
     rows_recv = int(stats.sum().item())
     touched = int((stats > 0).sum().item())
-    gemm1_ms = max_over_ranks(acc["gemm1"])
+    gemm1_ms = max_over_ranks(acc["gemm1"] if staged else acc["fused"])
     # algorithmic bytes of one GEMM1 launch: FP8 gate+up weights and their scales of the touched experts, the received
     # FP8 rows with their 16-byte metadata, the bf16 activations written
     gemm1_bytes = touched * (2 * I * H + 4 * 2 * I) + rows_recv * (H + 16) + rows_recv * I * 2
+    kernel_name = "grouped_gemm_kernel<0> (GEMM1 + SwiGLU)"
+    traffic = GEMM1_DRAM_TRAFFIC_BYTES_PER_EXPERT * touched
+    if not staged:
+        # the single fused launch moves the whole layer's bytes (formula of the reference's own test,
+        # tests/test_mega_moe_dcu.py:352-364): weights + scales, FP8 rows in, FP8 activations written and read, bf16 rows out
+        kernel_name = "mega_moe_fused_kernel (whole layer)"
+        gemm1_bytes = touched * (3 * H * I + 4 * (2 * I + H)) + rows_recv * (H + 4) + rows_recv * (I + 4) * 2 + rows_recv * H * 2
+        traffic = None
     hbm_peak, peak_kind = measured_peaks()
     achieved = gemm1_bytes / (gemm1_ms * 1e-3) / 1e9
 
@@ -310,14 +323,14 @@ def main():
         "data": "synthetic",
         "config": {"workload": f"DSV4-Flash MoE layer: {E} experts top-{K} hidden {H} intermediate {I}, {T} tokens/rank, EP={world}, "
                                "uniform N(0,1)-logit routing, W8A8 channelwise", "tokens_per_rank": T, "ep": world,
-                   "l2": "weights streamed per step exceed L2 (no flush needed)", "variant": "staged"},
+                   "l2": "weights streamed per step exceed L2 (no flush needed)", "variant": "staged" if staged else "fused"},
         "fp8_tflops": total_rows * FLOP_PER_ROW / (ms_step * 1e-3) / 1e12,
         "e2e": {"value": T * world / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_ms},
         "gpu_launches": launches,
         "clocks": clocks,
-        "roofline": {"kernel": "grouped_gemm_kernel<0> (GEMM1 + SwiGLU)", "bound": "hbm", "achieved": achieved, "peak": hbm_peak,
-                     "unit": "GB/s", "frac": achieved / hbm_peak, "peak_kind": f"of {peak_kind}", "traffic": GEMM1_DRAM_TRAFFIC_BYTES_PER_EXPERT * touched,
+        "roofline": {"kernel": kernel_name, "bound": "hbm", "achieved": achieved, "peak": hbm_peak,
+                     "unit": "GB/s", "frac": achieved / hbm_peak, "peak_kind": f"of {peak_kind}", "traffic": traffic,
                      "algorithmic_bytes": gemm1_bytes, "ms": gemm1_ms},
         "stage_ms": {k_: round(v, 4) for k_, v in acc.items()},
     }

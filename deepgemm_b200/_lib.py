@@ -35,6 +35,8 @@ _SIGNATURES = {
     "mm_ipc_free": (c_int, [c_void_p]),
     "mm_init_buffers": (c_int, [c_void_p, c_void_p, POINTER(c_uint64), c_int] + [c_int] * 6 + [c_void_p]),
     "mm_quant_per_token": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p]),
+    "mm_fp8_mma_peak_probe": (c_int, [c_int, c_void_p, c_void_p, POINTER(ctypes.c_double)]),
+    "mm_router_topk_quant": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "mm_fp8_w8a8_mega_moe": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                      POINTER(c_uint64), c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
                                      c_int, c_void_p, c_void_p]),
@@ -106,6 +108,25 @@ def stage_times() -> dict:
     buf = (c_float * len(STAGE_NAMES))()
     check(lib().mm_get_stage_times(buf, len(STAGE_NAMES)))
     return {n: float(v) for n, v in zip(STAGE_NAMES, buf) if v >= 0}
+
+
+def fp8_mma_peak_tflops(iters: int = 20000, repeats: int = 5) -> float:
+    """Dense FP8 tensor-core rate (TFLOP/s) measured with the library's probe kernel on the current device (best of repeats)."""
+    import torch
+    status = torch.zeros((1,), dtype=torch.int32, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    flops = ctypes.c_double()
+    best = 0.0
+    for _ in range(repeats + 1):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        check(lib().mm_fp8_mma_peak_probe(iters, status.data_ptr(), stream, ctypes.byref(flops)))
+        e1.record()
+        torch.cuda.synchronize()
+        best = max(best, flops.value / (e0.elapsed_time(e1) * 1e-3) / 1e12)
+    if int(status.item()) != 0:
+        raise MegaMoeError("the FP8 peak probe timed out")
+    return best
 
 
 def launch_count() -> int:

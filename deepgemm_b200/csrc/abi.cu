@@ -15,6 +15,7 @@
 #include "gemm.cuh"
 #include "layout.h"
 #include "misc.cuh"
+#include "probe.cuh"
 #include "route.cuh"
 
 static_assert(MM_ABI_MAX_RANKS == MM_MAX_RANKS, "header and layout disagree");
@@ -277,6 +278,40 @@ int mm_quant_per_token(const void* x_bf16, int64_t rows, int k, void* out_fp8, f
     if (blocks > (int64_t)sms * 8) blocks = (int64_t)sms * 8;
     mm::quant_per_token_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream_)>>>(
         static_cast<const __nv_bfloat16*>(x_bf16), rows, k, static_cast<uint8_t*>(out_fp8), out_scale);
+    MM_LAUNCHED();
+    return 0;
+}
+
+int mm_fp8_mma_peak_probe(int iters, int* status_dev, void* stream_, double* flops_out) {
+    MM_REQUIRE(iters > 0 && status_dev, "mm_fp8_mma_peak_probe: bad arguments");
+    int sms = 0;
+    if (int rc = sm_count(&sms)) return rc;
+    static bool attr_done = false;
+    if (!attr_done) {
+        MM_CUDA(cudaFuncSetAttribute(mm::fp8_mma_peak_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, mm::kABytes + mm::kBBytes));
+        attr_done = true;
+    }
+    mm::fp8_mma_peak_kernel<<<sms, 128, mm::kABytes + mm::kBBytes, static_cast<cudaStream_t>(stream_)>>>(iters, status_dev);
+    MM_LAUNCHED();
+    if (flops_out) *flops_out = (double)sms * iters * 8.0 * 2.0 * mm::kBlockM * mm::kBlockN * 32.0;
+    return 0;
+}
+
+int mm_router_topk_quant(const void* x_bf16, const float* router_logits, int num_tokens, int E, int K, int H, void* x_fp8,
+                         float* x_sf, int64_t* topk_idx, float* topk_weights, void* stream_) {
+    MM_REQUIRE(num_tokens >= 0 && E > 0 && E <= MM_MAX_EXPERTS && K > 0 && K <= MM_MAX_TOPK && K <= E && H > 0 && H % 8 == 0,
+               "mm_router_topk_quant: need 0 < K <= min(E, %d), E <= %d, H %% 8 == 0", MM_MAX_TOPK, MM_MAX_EXPERTS);
+    if (num_tokens == 0) return 0;
+    MM_REQUIRE(x_bf16 && router_logits && x_fp8 && x_sf && topk_idx && topk_weights, "mm_router_topk_quant: null pointer");
+    MM_REQUIRE((reinterpret_cast<uintptr_t>(x_bf16) & 15) == 0 && (reinterpret_cast<uintptr_t>(x_fp8) & 7) == 0,
+               "mm_router_topk_quant: x must be 16-byte aligned, x_fp8 8-byte aligned");
+    int sms = 0;
+    if (int rc = sm_count(&sms)) return rc;
+    int blocks = (num_tokens + 7) / 8;
+    if (blocks > sms * 8) blocks = sms * 8;
+    mm::router_topk_quant_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream_)>>>(
+        static_cast<const __nv_bfloat16*>(x_bf16), router_logits, num_tokens, E, K, H, static_cast<uint8_t*>(x_fp8), x_sf, topk_idx,
+        topk_weights);
     MM_LAUNCHED();
     return 0;
 }

@@ -47,7 +47,7 @@ struct MmSymLayout {
     int64_t signals;            // int32  [MM_NUM_BARRIERS][MM_MAX_RANKS]
     int64_t runtime_num_tokens; // int32  [1]  (device-side token count used in graph mode)
     int64_t count_matrix;       // int32  [R][E]   row r is written by rank r
-    int64_t pool_arrive;        // int32  [pool_rows / MM_BLOCK_M]  rows landed per m-block (fused variant), self-resetting
+    int64_t pool_arrive;        // int32  [pool_rows / MM_BLOCK_M + 1]  rows landed per m-block, last word = all rows (fused variant)
     int64_t x;                  // fp8    [T][H]
     int64_t x_sf;               // f32    [T]
     int64_t topk_idx;           // int64  [T][K]
@@ -71,7 +71,7 @@ struct MmScratchLayout {
     int64_t mblock_valid;  // int32 [pool_rows / MM_BLOCK_M]
     int64_t l1_done;       // int32 [4 * pool_rows / MM_BLOCK_M]  GEMM1 tiles finished per (m-block, 32-row quarter) (fused)
     int64_t l2_ready;      // int32 [pool_rows / MM_BLOCK_M]      quarters of an m-block requantised (fused)
-    int64_t grid_sync;     // int32 [4]  [0] CTA arrivals (monotonic), [1] fused calls completed
+    int64_t grid_sync;     // int32 [4]  [0] CTA arrivals (monotonic), [1] fused calls completed, [2] m-blocks requantised
     int64_t dest_row;      // int32 [T][K]   pool row of each local route (-1 invalid); kept for inspection
     int64_t row_amax;      // u32   [pool_rows]  bit pattern of the non-negative row amax, self-resetting
     int64_t act_scale;     // f32   [pool_rows]
@@ -95,7 +95,7 @@ static inline MmSymLayout mm_sym_layout(int R, int E, int T, int K, int H, int I
     L.runtime_num_tokens = o; o = mm_align(o + 16, 256);
     L.count_matrix = o;       o = mm_align(o + (int64_t)4 * R * E, 256);
     L.pool_rows = mm_pool_rows(R, E, T, K);
-    L.pool_arrive = o;        o = mm_align(o + L.pool_rows / MM_BLOCK_M * 4, 256);
+    L.pool_arrive = o;        o = mm_align(o + (L.pool_rows / MM_BLOCK_M + 1) * 4, 256);
     L.x = o;                  o = mm_align(o + (int64_t)T * H, 256);
     L.x_sf = o;               o = mm_align(o + (int64_t)T * 4, 256);
     L.topk_idx = o;           o = mm_align(o + (int64_t)T * K * 8, 256);

@@ -168,3 +168,82 @@ __global__ void __launch_bounds__(256, 4) combine_reduce_kernel(const uint8_t* _
 }
 
 }  // namespace mm
+
+namespace mm {
+
+// Upstream of the layer, in one kernel: router top-k + weight normalisation + per-token FP8 quantisation, written
+// straight into the symmetric buffer views (x, x_sf, topk_idx, topk_weights).  The reference leaves these steps to the
+// caller (torch.topk, softmax over the selected scores, cast_to_fp8_channelwise, four copy_ calls:
+// tests/test_mega_moe_dcu.py:491-508).  One warp per token.
+//   topk: the K largest logits, ties broken towards the lower expert index, listed in descending order;
+//   weights: softmax over the K selected logits (== full softmax renormalised to sum 1).
+__global__ void __launch_bounds__(256) router_topk_quant_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ logits,
+                                                               int num_tokens, int E, int K, int H, uint8_t* __restrict__ x_q,
+                                                               float* __restrict__ x_sf, int64_t* __restrict__ topk_idx,
+                                                               float* __restrict__ topk_w) {
+    const int lane = threadIdx.x & 31;
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int nwarps = (gridDim.x * blockDim.x) >> 5;
+    constexpr int kPer = MM_MAX_EXPERTS / 32;
+    for (int t = warp; t < num_tokens; t += nwarps) {
+        // ---- router: expert (lane + 32 * i) lives in v[i]
+        float v[kPer];
+#pragma unroll
+        for (int i = 0; i < kPer; ++i) {
+            const int e = lane + 32 * i;
+            v[i] = e < E ? logits[static_cast<int64_t>(t) * E + e] : -INFINITY;
+        }
+        float sel_val = 0.0f, denom = 0.0f, top = 0.0f;
+        int sel_idx = 0;
+        for (int k = 0; k < K; ++k) {
+            float best = -INFINITY;
+            int best_e = 0x7fffffff;
+#pragma unroll
+            for (int i = 0; i < kPer; ++i) {
+                const int e = lane + 32 * i;
+                if (v[i] > best) { best = v[i]; best_e = e; }      // within a lane experts ascend, so '>' keeps the lowest index
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+                if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+            }
+            if (k == 0) top = best;
+            const float p = expf(best - top);
+            denom += p;
+            if (lane == k) { sel_val = p; sel_idx = best_e; }
+            if ((best_e & 31) == lane) {
+#pragma unroll
+                for (int i = 0; i < kPer; ++i) if (i == (best_e >> 5)) v[i] = -INFINITY;   // remove the winner
+            }
+        }
+        if (lane < K) {
+            topk_idx[static_cast<int64_t>(t) * K + lane] = sel_idx;
+            topk_w[static_cast<int64_t>(t) * K + lane] = __fdiv_rn(sel_val, denom);
+        }
+        // ---- per-token FP8 quantisation (same arithmetic as quant_per_token_kernel)
+        const int vecs = H / 8;
+        const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<int64_t>(t) * H);
+        float amax = 0.0f;
+        for (int j = lane; j < vecs; j += 32) {
+            const uint4 d = src[j];
+            const uint32_t w[4] = {d.x, d.y, d.z, d.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) amax = fmaxf(amax, fmaxf(fabsf(bf16_lo(w[i])), fabsf(bf16_hi(w[i]))));
+        }
+        amax = warp_max(amax);
+        const float s = __fdiv_rn(fmaxf(amax, 1.0e-4f), 448.0f);
+        if (lane == 0) x_sf[t] = s;
+        uint2* dst = reinterpret_cast<uint2*>(x_q + static_cast<int64_t>(t) * H);
+        for (int j = lane; j < vecs; j += 32) {
+            const uint4 d = src[j];
+            uint2 o;
+            o.x = pack4_e4m3(__fdiv_rn(bf16_lo(d.x), s), __fdiv_rn(bf16_hi(d.x), s), __fdiv_rn(bf16_lo(d.y), s), __fdiv_rn(bf16_hi(d.y), s));
+            o.y = pack4_e4m3(__fdiv_rn(bf16_lo(d.z), s), __fdiv_rn(bf16_hi(d.z), s), __fdiv_rn(bf16_lo(d.w), s), __fdiv_rn(bf16_hi(d.w), s));
+            dst[j] = o;
+        }
+    }
+}
+
+}  // namespace mm

@@ -513,6 +513,29 @@ def fp8_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer: SymmBuffer
 fp8_w8a8_mega_moe = fp8_mega_moe
 
 
+def fill_inputs_from_router(sym_buffer: SymmBuffer, x: torch.Tensor, router_logits: torch.Tensor) -> int:
+    """Fill sym_buffer.x / x_sf / topk_idx / topk_weights from bf16 activations [T, H] and fp32 router logits [T, E] with
+    one kernel: top-k (descending, ties to the lower index), softmax over the selected logits, per-token FP8 cast.
+    The reference leaves this to the caller as torch.topk + softmax + cast_to_fp8_channelwise + four copies
+    (tests/test_mega_moe_dcu.py:491-508).  Returns the number of tokens written."""
+    sb = sym_buffer
+    _require_cuda(x, "x")
+    _require_cuda(router_logits, "router_logits")
+    if x.dtype != torch.bfloat16 or x.dim() != 2 or x.size(1) != sb.hidden:
+        raise ValueError("x must be bf16 [tokens, hidden]")
+    if router_logits.dtype != torch.float32 or tuple(router_logits.shape) != (x.size(0), sb.num_experts):
+        raise ValueError("router_logits must be fp32 [tokens, num_experts]")
+    if x.size(0) > sb.num_max_tokens_per_rank:
+        raise ValueError("too many tokens")
+    x = x.contiguous()
+    router_logits = router_logits.contiguous()
+    with torch.cuda.device(sb.device):
+        _lib.check(_lib.lib().mm_router_topk_quant(x.data_ptr(), router_logits.data_ptr(), x.size(0), sb.num_experts, sb.num_topk,
+                                                  sb.hidden, sb.x.data_ptr(), sb.x_sf.data_ptr(), sb.topk_idx.data_ptr(),
+                                                  sb.topk_weights.data_ptr(), _stream_ptr()))
+    return int(x.size(0))
+
+
 def deepep_deepgemm_preprocess_channelwise(*args, **kwargs):
     raise NotImplementedError("DeepEP-layout pre-processing helpers are not part of this build")
 
@@ -535,4 +558,5 @@ __all__ = [
     "deepep_deepgemm_postprocess_channelwise",
     "fp8_mega_moe",
     "fp8_w8a8_mega_moe",
+    "fill_inputs_from_router",
 ]

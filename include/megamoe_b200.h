@@ -75,6 +75,14 @@ int mm_init_buffers(void* sym_base, void* scratch, const uint64_t* peer_ptrs, in
  * Replaces cast_to_fp8_channelwise, megamoe/__init__.py:51-56 (bit-exact codes and scales). */
 int mm_quant_per_token(const void* x_bf16, int64_t rows, int k, void* out_fp8, float* out_scale, void* stream);
 
+/* Router top-k + weight normalisation + per-token FP8 quantisation in one kernel, writing the four input views of the
+ * symmetric buffer directly (pass their device addresses).  router_logits f32 [num_tokens, E]; the K largest logits are
+ * selected (ties towards the lower index, descending order) and weighted with a softmax over the selected logits.
+ * Replaces what the reference leaves to its caller: torch.topk + softmax + cast_to_fp8_channelwise + four copy_ calls
+ * (tests/test_mega_moe_dcu.py:491-508, README.md:482-487). */
+int mm_router_topk_quant(const void* x_bf16, const float* router_logits, int num_tokens, int E, int K, int H, void* x_fp8,
+                         float* x_sf, int64_t* topk_idx, float* topk_weights, void* stream);
+
 /* The layer.  Inputs x / x_sf / topk_idx / topk_weights are read from the symmetric buffer views; y receives
  * bf16 [num_tokens, H].  w1 = fp8 weights [E_loc, 2I, H] (rows [0,I) gate, [I,2I) up) with s1 f32 [E_loc, 2I]; w2 = fp8
  * weights [E_loc, H, I] with s2 f32 [E_loc, H].  Both weight tensors are stored TILED in the order the GEMM kernels
@@ -126,6 +134,12 @@ int mm_fp8_w8a8_mega_moe_static(void* y, const void* x_fp8, const float* x_sf, c
                                 const float* topk_weights, const void* w1, const float* s1, const void* w2, const float* s2,
                                 int* stats, int num_tokens, int num_experts, int K, int H, int I, float activation_clamp,
                                 void* stream);
+
+/* Measurement aid (no counterpart in the reference, whose test divides by a datasheet figure, tests/test_mega_moe_dcu.py:20-22):
+ * launch a kernel that issues `iters` groups of eight dense FP8 MMAs (tcgen05 kind::f8f6f4, M128 x N256 x K32) per SM from
+ * operands resident in shared memory.  *flops_out receives the floating-point operations of the launch; time it with events
+ * on `stream` to get the tensor-core rate the GEMM kernels can at best reach.  status_dev: a zeroed device int. */
+int mm_fp8_mma_peak_probe(int iters, int* status_dev, void* stream, double* flops_out);
 
 /* Per-stage device timing of the layer call (the reference's test prints per-kernel times with a profiler,
  * tests/test_mega_moe_dcu.py:794-834; here CUDA events are recorded on the caller's stream around every launch).

@@ -239,6 +239,33 @@ def test_dsv4_shaped_slice():
     _check_case(mc.make_case(1, 16, 6, 4096, 2048, [512], seed=10))
 
 
+def test_router_topk_and_quantisation_fill_the_buffer_in_one_kernel():
+    """Indices equal torch.topk exactly (seeded logits have no ties), weights equal the softmax over the selected logits
+    to fp32 rounding, FP8 codes and scales bit-exact; the layer run on the filled buffer matches the oracle."""
+    import megamoe
+    E, K, H, I, T = 64, 6, 1024, 512, 300
+    g = torch.Generator().manual_seed(17)
+    x = orc.make_inputs(T, H, seed=17)
+    logits = torch.randn((T, E), generator=g)
+    sb = megamoe.get_symm_buffer_for_mega_moe(None, E, T, K, H, I)
+    assert megamoe.fill_inputs_from_router(sb, x.cuda(), logits.cuda()) == T
+    vals, idx = torch.topk(logits, K, dim=-1)
+    w = torch.softmax(vals, dim=-1)
+    assert torch.equal(sb.topk_idx[:T].cpu(), idx)
+    assert torch.allclose(sb.topk_weights[:T].cpu(), w, rtol=1e-5, atol=1e-7)
+    q_ref, s_ref = orc.cast_to_fp8_channelwise(x)
+    assert torch.equal(sb.x[:T].cpu().view(torch.uint8), q_ref.view(torch.uint8)) and torch.equal(sb.x_sf[:T].cpu(), s_ref)
+    w1b, w2b = orc.make_weights(E, H, I, seed=18)
+    l1, l2 = megamoe.transform_fp8_weights_for_mega_moe(w1b.cuda(), w2b.cuda())
+    y = torch.empty((T, H), dtype=torch.bfloat16, device="cuda")
+    megamoe.fp8_w8a8_mega_moe(y, l1, l2, sb)
+    sb.check_status()
+    w1q, w1s = orc.cast_grouped_weight_to_fp8_channelwise(w1b); w2q, w2s = orc.cast_grouped_weight_to_fp8_channelwise(w2b)
+    ys, _, _ = orc.moe_layer([q_ref], [s_ref], [idx], [sb.topk_weights[:T].cpu()], [w1q], [w1s], [w2q], [w2s], E)
+    mc.assert_end_to_end_close(y.cpu(), ys[0], "layer on router-filled inputs")
+    sb.destroy()
+
+
 def test_api_argument_errors():
     import megamoe
     case = mc.make_case(1, 8, 2, 512, 256, [16], seed=11)

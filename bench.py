@@ -300,16 +300,18 @@ def main():
     megamoe.fp8_w8a8_mega_moe(y, l1, l2, sb, cumulative_local_expert_recv_stats=stats)
     rows_recv = int(stats.sum().item())
     touched = int((stats > 0).sum().item())
-    gemm1_ms = max_over_ranks(acc["gemm1"] if staged else acc["fused"])
+    split = "gemm1" in acc        # staged: GEMM1 / requant / GEMM2 / reduce are separate launches (unless MEGAMOE_STAGED_MERGED=1)
+    gemm1_ms = max_over_ranks(acc["gemm1"] if split else acc["fused"])
     # algorithmic bytes of one GEMM1 launch: FP8 gate+up weights and their scales of the touched experts, the received
     # FP8 rows with their 16-byte metadata, the bf16 activations written
     gemm1_bytes = touched * (2 * I * H + 4 * 2 * I) + rows_recv * (H + 16) + rows_recv * I * 2
     kernel_name = "grouped_gemm_kernel<0> (GEMM1 + SwiGLU)"
     traffic = GEMM1_DRAM_TRAFFIC_BYTES_PER_EXPERT * touched
-    if not staged:
-        # the single fused launch moves the whole layer's bytes (formula of the reference's own test,
+    if not split:
+        # the persistent kernel moves the whole layer's bytes (formula of the reference's own test,
         # tests/test_mega_moe_dcu.py:352-364): weights + scales, FP8 rows in, FP8 activations written and read, bf16 rows out
-        kernel_name = "mega_moe_fused_kernel (whole layer)"
+        kernel_name = ("mega_moe_fused_kernel (GEMM1 + requantisation + GEMM2 + combine reduce)" if staged
+                       else "mega_moe_fused_kernel (whole layer)")
         gemm1_bytes = touched * (3 * H * I + 4 * (2 * I + H)) + rows_recv * (H + 4) + rows_recv * (I + 4) * 2 + rows_recv * H * 2
         traffic = None
     hbm_peak, peak_kind = measured_peaks()

@@ -5,6 +5,7 @@
 #include <stdarg.h>
 #include <stdio.h>
 #include <string.h>
+#include <stdlib.h>
 
 #include <atomic>
 #include <mutex>
@@ -379,30 +380,38 @@ int mm_fp8_w8a8_mega_moe(void* y, const void* w1, const float* s1, const void* w
     g1.kdim = H; g1.n_blocks = I / 128; g1.n_out = I; g1.w_rows_per_expert = 2 * I; g1.w_scale = s1;
     g2.kdim = I; g2.n_blocks = (H + mm::kBlockN - 1) / mm::kBlockN; g2.n_out = H; g2.w_rows_per_expert = H; g2.w_scale = s2;
 
+    mm::FusedParams fp;
+    memset(&fp, 0, sizeof(fp));
+    fp.rp = rp;
+    fp.g1 = g1;
+    fp.g2 = g2;
+    fp.y = static_cast<__nv_bfloat16*>(y);
+    fp.l1_done = reinterpret_cast<int*>(sc + rp.cl.l1_done);
+    fp.l2_ready = reinterpret_cast<int*>(sc + rp.cl.l2_ready);
+    fp.grid_sync = reinterpret_cast<int*>(sc + rp.cl.grid_sync);
+    fp.act_fp8 = sc + rp.cl.act_fp8;
+    fp.act_scale_w = reinterpret_cast<float*>(sc + rp.cl.act_scale);
+    // a wave holds enough GEMM1 tiles for about two rounds over the SMs, so its requantisation is done when its GEMM2 starts
+    fp.wave_mblocks = (2 * sms + g1.n_blocks - 1) / g1.n_blocks;
+    if (const char* v = getenv("MEGAMOE_WAVE_MBLOCKS")) { const int w = atoi(v); fp.wave_mblocks = w > 0 ? w : (1 << 28); }   // tuning aid
+    void* fused_args[] = {&tm_pool, &tm_w1, &tm_act, &tm_w2, &fp};
+
     if (mode == MM_MODE_FUSED) {
         MM_REQUIRE(tokens_bound * K <= mm::kFusedMaxRoutes,
                    "the fused variant holds at most %d routes (tokens x top-k) per rank; use the staged variant", mm::kFusedMaxRoutes);
-        mm::FusedParams fp;
-        memset(&fp, 0, sizeof(fp));
-        fp.rp = rp;
-        fp.g1 = g1;
-        fp.g2 = g2;
-        fp.y = static_cast<__nv_bfloat16*>(y);
-        fp.l1_done = reinterpret_cast<int*>(sc + rp.cl.l1_done);
-        fp.l2_ready = reinterpret_cast<int*>(sc + rp.cl.l2_ready);
-        fp.grid_sync = reinterpret_cast<int*>(sc + rp.cl.grid_sync);
-        fp.act_fp8 = sc + rp.cl.act_fp8;
-        fp.act_scale_w = reinterpret_cast<float*>(sc + rp.cl.act_scale);
         if (int rc = stage_begin(stream)) return rc;
-        void* args[] = {&tm_pool, &tm_w1, &tm_act, &tm_w2, &fp};
         // cooperative launch: all CTAs must be resident because they wait on one another
         MM_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(mm::mega_moe_fused_kernel), dim3(sms), dim3(mm::kFusedThreads),
-                                            args, mm::kGemmSmemBytes, stream));
+                                            fused_args, mm::kGemmSmemBytes, stream));
         MM_LAUNCHED();
         if (int rc = stage_end(MM_STAGE_FUSED, stream)) return rc;
         return 0;
     }
 
+    // Staged variant: GEMM1, requantisation, GEMM2, combine barrier and reduce are separate launches.  Measured on B200 this
+    // beats running them as one cooperative kernel (gemm_only mode of the fused kernel, MEGAMOE_STAGED_MERGED=1) at
+    // 4096-8192 tokens: there the in-epilogue requantisation and per-m-block dependency checks cost more than the launches.
+    static const bool split_gemms = [] { const char* v = getenv("MEGAMOE_STAGED_MERGED"); return !(v && v[0] == '1'); }();
     if (int rc = stage_begin(stream)) return rc;
 #define MM_STAGE(id) do { MM_LAUNCHED(); if (int rc_ = stage_end(id, stream)) return rc_; } while (0)
     mm::route_count_kernel<<<route_blocks, MM_ROUTE_CHUNK, 0, stream>>>(rp);
@@ -416,6 +425,13 @@ int mm_fp8_w8a8_mega_moe(void* y, const void* w1, const float* s1, const void* w
     if (R > 1) {
         mm::rank_barrier_kernel<<<1, 32, 0, stream>>>(rp, MM_BAR_DISPATCH);
         MM_STAGE(MM_STAGE_BARRIER_DISPATCH);
+    }
+    if (!split_gemms) {
+        fp.gemm_only = 1;
+        MM_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(mm::mega_moe_fused_kernel), dim3(sms), dim3(mm::kFusedThreads),
+                                            fused_args, mm::kGemmSmemBytes, stream));
+        MM_STAGE(MM_STAGE_FUSED);
+        return 0;
     }
     mm::grouped_gemm_kernel<0><<<sms, mm::kGemmThreads, mm::kGemmSmemBytes, stream>>>(tm_pool, tm_w1, g1);
     MM_STAGE(MM_STAGE_GEMM1);

@@ -35,6 +35,8 @@ struct FusedParams {
     int* grid_sync;        // [0] CTA arrivals (monotonic), [1] fused calls completed
     uint8_t* act_fp8;      // [pool_rows][I]
     float* act_scale_w;    // writable alias of g2.act_scale
+    int wave_mblocks;      // m-blocks per wave of the tile order (see decode_tile)
+    int gemm_only;         // 1: routing and dispatch were done by the staged kernels (and a dispatch barrier); start at the tile loop
 };
 
 // shared-memory scratch of the routing phases, aliased onto the (not yet used) operand ring
@@ -109,7 +111,7 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
     }
     if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), 512); tmem_relinquish(); }
     // the epoch words are only rewritten at the very end of the kernel, after every CTA has passed the grid barrier
-    const int epoch = reinterpret_cast<const int*>(rp.scratch + rp.cl.epoch)[0] + 1;
+    const int epoch = reinterpret_cast<const int*>(rp.scratch + rp.cl.epoch)[0] + (fp.gemm_only ? 0 : 1);
     const int fused_calls = fp.grid_sync[1];
     const int n_tokens = route_num_tokens(rp);
     const int n_routes = n_tokens * rp.K;
@@ -119,6 +121,7 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
+    if (!fp.gemm_only) {
     // ------------------------------------------------------------------ phase 1: local histogram, publish counts
     {
         const int64_t* idx = reinterpret_cast<const int64_t*>(rp.sym + rp.sl.topk_idx);
@@ -216,6 +219,9 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
             }
         }
     }
+    } else if (tid == 0) {
+        s_misc[0] = fp.g1.plan[0];      // the plan was made by route_plan_kernel
+    }
     __threadfence();
     __syncthreads();
     if (tid == 0) stamp(5);
@@ -225,7 +231,7 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
     const int arrive_total_slot = static_cast<int>(rp.sl.pool_rows / MM_BLOCK_M);   // last word of the arrival array
 
     // ------------------------------------------------------------------ phase 3: push this CTA's share of the rows
-    if (healthy) {
+    if (healthy && !fp.gemm_only) {
         const uint8_t* x = rp.sym + rp.sl.x;
         const float* x_sf = reinterpret_cast<const float*>(rp.sym + rp.sl.x_sf);
         const float* tw = reinterpret_cast<const float*>(rp.sym + rp.sl.topk_weights);
@@ -288,8 +294,41 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
     // ------------------------------------------------------------------ phase 4: GEMM1 tiles, then GEMM2 tiles
     const GemmParams& g1 = fp.g1;
     const GemmParams& g2 = fp.g2;
-    const int tiles1 = healthy ? num_mblocks * g1.n_blocks : 0;
-    const int tiles_all = healthy ? tiles1 + num_mblocks * g2.n_blocks : 0;
+    // Tile order: m-blocks are grouped in waves of `wave_mblocks`; the global order is
+    //     G1(0), G1(1), G2(0), G1(2), G2(1), ..., G1(n-1), G2(n-2), G2(n-1)
+    // (G1(k) / G2(k) = all GEMM1 / GEMM2 tiles of wave k).  Interleaving the two GEMMs spreads the combine stores (NVLink)
+    // over the whole compute phase; putting G2(k) after G1(k+1) gives the requantisation of wave k a full wave of slack.
+    // A GEMM2 tile only ever waits for GEMM1 tiles that come earlier in this order, so the waits cannot form a cycle.
+    const int nb1 = g1.n_blocks, nb2 = g2.n_blocks;
+    const int wave_m = max(1, fp.wave_mblocks);
+    const int n_waves = (num_mblocks + wave_m - 1) / wave_m;
+    auto decode_tile = [&](int tile, bool& second, int& mb, int& nb) {
+        const int A = wave_m * nb1, B = wave_m * nb2;                       // tiles of a full wave
+        const int last_m = num_mblocks - (n_waves - 1) * wave_m;            // m-blocks of the last wave
+        int wave, r;
+        if (n_waves == 1) {
+            second = tile >= last_m * nb1; wave = 0; r = second ? tile - last_m * nb1 : tile;
+        } else if (tile < A) {
+            second = false; wave = 0; r = tile;
+        } else {
+            const int p = tile - A;
+            const int k = p / (A + B);
+            if (k < n_waves - 2) {                                          // block k = [G1(k+1), G2(k)], both full
+                r = p - k * (A + B);
+                second = r >= A; wave = second ? k : k + 1; if (second) r -= A;
+            } else {                                                        // tail: G1(n-1) (maybe partial), G2(n-2), G2(n-1)
+                r = p - (n_waves - 2) * (A + B);
+                const int a_last = last_m * nb1;
+                if (r < a_last) { second = false; wave = n_waves - 1; }
+                else if (r < a_last + B) { second = true; wave = n_waves - 2; r -= a_last; }
+                else { second = true; wave = n_waves - 1; r -= a_last + B; }
+            }
+        }
+        const int nbk = second ? nb2 : nb1;
+        mb = wave * wave_m + r / nbk;
+        nb = r - (r / nbk) * nbk;
+    };
+    const int tiles_all = healthy ? num_mblocks * (g1.n_blocks + g2.n_blocks) : 0;
     const int* arrive = reinterpret_cast<const int*>(rp.sym + rp.sl.pool_arrive);
 
     if (warp == 0) {
@@ -297,12 +336,11 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
         int stage = 0; uint32_t phase = 0;
         bool alive = true;
         // once every row has arrived (every m-block is requantised) no further per-tile polling is needed
-        bool all_arrived = false, all_ready = false;
+        bool all_arrived = fp.gemm_only != 0, all_ready = false;
         for (int tile = blockIdx.x; tile < tiles_all && alive; tile += gridDim.x) {
-            const bool second = tile >= tiles1;
+            bool second; int mb, nb;
+            decode_tile(tile, second, mb, nb);
             const GemmParams& g = second ? g2 : g1;
-            const int t = second ? tile - tiles1 : tile;
-            const int mb = t / g.n_blocks, nb = t - mb * g.n_blocks;
             const int e = g.mblock_expert[mb];
             const int k_blocks = g.kdim / kBlockK;
             const int b_tile0 = (e * g.n_blocks + nb) * k_blocks;
@@ -350,7 +388,9 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
         int acc = 0; uint32_t acc_phase = 0;
         bool alive = true;
         for (int tile = blockIdx.x; tile < tiles_all && alive; tile += gridDim.x) {
-            const GemmParams& g = tile >= tiles1 ? g2 : g1;
+            bool second; int mb, nb;
+            decode_tile(tile, second, mb, nb);
+            const GemmParams& g = second ? g2 : g1;
             const int k_blocks = g.kdim / kBlockK;
             if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, g.timeout_ns)) { alive = false; break; }
             tc_fence_after();
@@ -384,10 +424,9 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
         bool alive = true;
         for (int tile = blockIdx.x; tile < tiles_all && alive; tile += gridDim.x) {
             if (*abort_flag != 0) break;
-            const bool second = tile >= tiles1;
+            bool second; int mb, nb;
+            decode_tile(tile, second, mb, nb);
             const GemmParams& g = second ? g2 : g1;
-            const int t = second ? tile - tiles1 : tile;
-            const int mb = t / g.n_blocks, nb = t - mb * g.n_blocks;
             const int e = g.mblock_expert[mb];
             const int valid = g.mblock_valid[mb];
             const int row = mb * kBlockM + et;
@@ -564,7 +603,7 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
         if (blockIdx.x == 0 && tid == 0) {
             arr[arrive_total_slot] = 0;
             fp.grid_sync[2] = 0;
-            reinterpret_cast<int*>(rp.scratch + rp.cl.epoch)[0] = epoch;
+            if (!fp.gemm_only) reinterpret_cast<int*>(rp.scratch + rp.cl.epoch)[0] = epoch;
             fp.grid_sync[1] = fused_calls + 1;
         }
     }

@@ -35,6 +35,8 @@ _SIGNATURES = {
     "mm_ipc_free": (c_int, [c_void_p]),
     "mm_init_buffers": (c_int, [c_void_p, c_void_p, POINTER(c_uint64), c_int] + [c_int] * 6 + [c_void_p]),
     "mm_quant_per_token": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p]),
+    "mm_deepep_scatter_channelwise": (c_int, [c_void_p] * 11 + [c_int] * 6 + [c_void_p]),
+    "mm_deepep_gather_channelwise": (c_int, [c_void_p] * 5 + [c_int] * 5 + [c_void_p]),
     "mm_fp8_mma_peak_probe": (c_int, [c_int, c_void_p, c_void_p, POINTER(ctypes.c_double)]),
     "mm_router_topk_quant": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "mm_fp8_w8a8_mega_moe": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,

@@ -12,6 +12,7 @@
 #include <vector>
 
 #include "../../include/megamoe_b200.h"
+#include "deepep_layout.cuh"
 #include "fused.cuh"
 #include "gemm.cuh"
 #include "layout.h"
@@ -279,6 +280,56 @@ int mm_quant_per_token(const void* x_bf16, int64_t rows, int k, void* out_fp8, f
     if (blocks > (int64_t)sms * 8) blocks = (int64_t)sms * 8;
     mm::quant_per_token_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream_)>>>(
         static_cast<const __nv_bfloat16*>(x_bf16), rows, k, static_cast<uint8_t*>(out_fp8), out_scale);
+    MM_LAUNCHED();
+    return 0;
+}
+
+int mm_deepep_scatter_channelwise(void* grouped_x, float* grouped_x_scale, float* route_weights, int* m_indices, int* output_index,
+                                  int* expert_start_loc, const void* recv_x, const float* recv_x_scale, const void* recv_topk_ids,
+                                  const float* recv_topk_weights, const int* num_recv_tokens_per_expert, int total_rows,
+                                  int recv_rows, int topk, int hidden, int num_experts, int topk_ids_i64, void* stream_) {
+    MM_REQUIRE(total_rows >= 0 && recv_rows >= 0 && topk > 0 && hidden > 0 && hidden % 16 == 0 && num_experts > 0,
+               "mm_deepep_scatter_channelwise: bad shape (hidden must be a multiple of 16)");
+    MM_REQUIRE(expert_start_loc && num_recv_tokens_per_expert, "mm_deepep_scatter_channelwise: null pointer");
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    mm::deepep_prefix_kernel<<<1, 1024, 0, stream>>>(num_recv_tokens_per_expert, expert_start_loc, num_experts);
+    MM_LAUNCHED();
+    const int64_t routes = (int64_t)recv_rows * topk;
+    if (routes == 0) return 0;
+    MM_REQUIRE(grouped_x && grouped_x_scale && route_weights && m_indices && output_index && recv_x && recv_x_scale && recv_topk_ids &&
+               recv_topk_weights, "mm_deepep_scatter_channelwise: null pointer");
+    const int blocks = (num_experts + 7) / 8;
+    if (topk_ids_i64)
+        mm::deepep_assign_kernel<int64_t><<<blocks, 256, 0, stream>>>(recv_topk_ids, expert_start_loc, output_index, m_indices, routes, num_experts, total_rows);
+    else
+        mm::deepep_assign_kernel<int32_t><<<blocks, 256, 0, stream>>>(recv_topk_ids, expert_start_loc, output_index, m_indices, routes, num_experts, total_rows);
+    MM_LAUNCHED();
+    int sms = 0;
+    if (int rc = sm_count(&sms)) return rc;
+    int64_t cblocks = (routes + 7) / 8;
+    if (cblocks > (int64_t)sms * 8) cblocks = (int64_t)sms * 8;
+    mm::deepep_scatter_rows_kernel<<<(unsigned)cblocks, 256, 0, stream>>>(static_cast<const uint8_t*>(recv_x), recv_x_scale, recv_topk_weights,
+                                                                         output_index, static_cast<uint8_t*>(grouped_x), grouped_x_scale,
+                                                                         route_weights, routes, topk, hidden);
+    MM_LAUNCHED();
+    return 0;
+}
+
+int mm_deepep_gather_channelwise(void* recv_y, const void* l2_out, const void* recv_topk_ids, const float* recv_topk_weights,
+                                 const int* output_index, int recv_rows, int topk, int hidden, int topk_ids_i64,
+                                 int apply_topk_weights, void* stream_) {
+    MM_REQUIRE(recv_rows >= 0 && topk > 0 && hidden > 0 && hidden % 8 == 0, "mm_deepep_gather_channelwise: bad shape (hidden must be a multiple of 8)");
+    if (recv_rows == 0) return 0;
+    MM_REQUIRE(recv_y && l2_out && recv_topk_ids && recv_topk_weights && output_index, "mm_deepep_gather_channelwise: null pointer");
+    int sms = 0;
+    if (int rc = sm_count(&sms)) return rc;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (topk_ids_i64)
+        mm::deepep_gather_kernel<int64_t><<<sms * 8, 256, 0, stream>>>(static_cast<__nv_bfloat16*>(recv_y), static_cast<const __nv_bfloat16*>(l2_out),
+                                                                      recv_topk_ids, recv_topk_weights, output_index, recv_rows, topk, hidden, apply_topk_weights);
+    else
+        mm::deepep_gather_kernel<int32_t><<<sms * 8, 256, 0, stream>>>(static_cast<__nv_bfloat16*>(recv_y), static_cast<const __nv_bfloat16*>(l2_out),
+                                                                      recv_topk_ids, recv_topk_weights, output_index, recv_rows, topk, hidden, apply_topk_weights);
     MM_LAUNCHED();
     return 0;
 }

@@ -536,12 +536,74 @@ def fill_inputs_from_router(sym_buffer: SymmBuffer, x: torch.Tensor, router_logi
     return int(x.size(0))
 
 
-def deepep_deepgemm_preprocess_channelwise(*args, **kwargs):
-    raise NotImplementedError("DeepEP-layout pre-processing helpers are not part of this build")
+def deepep_deepgemm_preprocess_channelwise(recv_x: torch.Tensor, recv_x_scale: torch.Tensor, recv_topk_ids: torch.Tensor,
+                                           recv_topk_weights: torch.Tensor, num_recv_tokens_per_expert: torch.Tensor,
+                                           all_tokens: int):
+    """Group DeepEP-received tokens by expert for a grouped GEMM (csrc/apis/mega_dcu.hpp:222-291): returns
+    (grouped_x fp8 [rows,H], grouped_x_scale f32 [rows], route_weights f32 [rows], m_indices i32 [rows],
+    output_index i32 [tokens, topk]) with rows = max(all_tokens, 1)."""
+    for t in (recv_x, recv_x_scale, recv_topk_ids, recv_topk_weights, num_recv_tokens_per_expert):
+        _require_cuda(t, "DeepEP preprocess tensors")
+        if not t.is_contiguous():
+            raise RuntimeError("DeepEP preprocess tensors must be contiguous")
+    if recv_x.dtype != torch.float8_e4m3fn:
+        raise RuntimeError("DeepEP preprocess expects FP8 E4M3 recv_x")
+    if recv_x_scale.dtype != torch.float32 or recv_topk_weights.dtype != torch.float32:
+        raise RuntimeError("DeepEP preprocess scales and weights must be FP32")
+    if recv_topk_ids.dtype not in (torch.int64, torch.int32):
+        raise RuntimeError("DeepEP preprocess topk ids must be int64 or int32")
+    if num_recv_tokens_per_expert.dtype != torch.int32:
+        raise RuntimeError("num_recv_tokens_per_expert must be int32")
+    if recv_x.dim() != 2 or recv_topk_ids.dim() != 2 or recv_topk_ids.shape != recv_topk_weights.shape:
+        raise RuntimeError("recv_x must be [tokens, hidden]; topk ids/weights must be [tokens, topk]")
+    if recv_topk_ids.size(0) != recv_x.size(0) or recv_x_scale.numel() != recv_x.size(0):
+        raise RuntimeError("topk rows and recv_x_scale must match recv_x")
+    if all_tokens < 0:
+        raise RuntimeError("all_tokens must be non-negative")
+    rows = max(int(all_tokens), 1)
+    recv_rows, hidden = recv_x.shape
+    topk = recv_topk_ids.size(1)
+    num_experts = num_recv_tokens_per_expert.numel()
+    dev = recv_x.device
+    grouped_x = torch.empty((rows, hidden), dtype=torch.float8_e4m3fn, device=dev)
+    grouped_x_scale = torch.empty((rows,), dtype=torch.float32, device=dev)
+    route_weights = torch.zeros((rows,), dtype=torch.float32, device=dev)
+    m_indices = torch.full((rows,), -1, dtype=torch.int32, device=dev)
+    output_index = torch.full((recv_rows, topk), -1, dtype=torch.int32, device=dev)
+    expert_start_loc = torch.empty((num_experts,), dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().mm_deepep_scatter_channelwise(
+            grouped_x.data_ptr(), grouped_x_scale.data_ptr(), route_weights.data_ptr(), m_indices.data_ptr(), output_index.data_ptr(),
+            expert_start_loc.data_ptr(), recv_x.data_ptr(), recv_x_scale.data_ptr(), recv_topk_ids.data_ptr(),
+            recv_topk_weights.data_ptr(), num_recv_tokens_per_expert.data_ptr(), rows, recv_rows, topk, hidden, num_experts,
+            1 if recv_topk_ids.dtype == torch.int64 else 0, _stream_ptr()))
+    return grouped_x, grouped_x_scale, route_weights, m_indices, output_index
 
 
-def deepep_deepgemm_postprocess_channelwise(*args, **kwargs):
-    raise NotImplementedError("DeepEP-layout post-processing helpers are not part of this build")
+def deepep_deepgemm_postprocess_channelwise(recv_y: torch.Tensor, l2_out: torch.Tensor, recv_topk_ids: torch.Tensor,
+                                            recv_topk_weights: torch.Tensor, output_index: torch.Tensor,
+                                            apply_topk_weights: bool = False) -> None:
+    """Sum the per-route grouped-GEMM outputs back per received token, in place into recv_y
+    (csrc/apis/mega_dcu.hpp:293-336)."""
+    for t in (recv_y, l2_out, recv_topk_ids, recv_topk_weights, output_index):
+        _require_cuda(t, "DeepEP postprocess tensors")
+        if not t.is_contiguous():
+            raise RuntimeError("DeepEP postprocess tensors must be contiguous")
+    if recv_y.dtype != torch.bfloat16 or l2_out.dtype != torch.bfloat16:
+        raise RuntimeError("DeepEP postprocess expects BF16 tensors")
+    if recv_topk_ids.dtype not in (torch.int64, torch.int32):
+        raise RuntimeError("DeepEP postprocess topk ids must be int64 or int32")
+    if recv_topk_weights.dtype != torch.float32 or output_index.dtype != torch.int32:
+        raise RuntimeError("topk weights must be FP32 and output_index int32")
+    if (recv_y.dim() != 2 or l2_out.dim() != 2 or recv_topk_ids.shape != recv_topk_weights.shape
+            or recv_topk_ids.shape != output_index.shape or recv_y.size(0) != recv_topk_ids.size(0)
+            or recv_y.size(1) != l2_out.size(1)):
+        raise RuntimeError("DeepEP postprocess shape mismatch")
+    with torch.cuda.device(recv_y.device):
+        _lib.check(_lib.lib().mm_deepep_gather_channelwise(
+            recv_y.data_ptr(), l2_out.data_ptr(), recv_topk_ids.data_ptr(), recv_topk_weights.data_ptr(), output_index.data_ptr(),
+            recv_y.size(0), recv_topk_ids.size(1), recv_y.size(1), 1 if recv_topk_ids.dtype == torch.int64 else 0,
+            1 if apply_topk_weights else 0, _stream_ptr()))
 
 
 __all__ = [

@@ -135,6 +135,21 @@ int mm_fp8_w8a8_mega_moe_static(void* y, const void* x_fp8, const float* x_sf, c
                                 int* stats, int num_tokens, int num_experts, int K, int H, int I, float activation_clamp,
                                 void* stream);
 
+/* DeepEP-layout helpers of the reference's split baseline (DeepEP dispatch -> scatter -> grouped GEMM -> gather -> DeepEP
+ * combine).  Scatter groups the received tokens by expert: expert_start_loc = exclusive prefix of
+ * num_recv_tokens_per_expert; route (token, slot) with expert e gets row expert_start_loc[e] + its rank among e's routes (in
+ * route order; the reference's atomicAdd order is unspecified); output_index[route] = row or -1; m_indices[row] = e; the FP8
+ * row, its scale and the route weight are copied.  The caller pre-fills output_index and m_indices with -1 and
+ * route_weights with 0.  Gather: recv_y[token] = bf16(sum over slots of l2_out[output_index] (* weight)).
+ * Replace launch_mega_moe_deepep_scatter_channelwise_hip / ..._gather_..., csrc/kernels/mega_moe_baseline_hip.cu:130-232. */
+int mm_deepep_scatter_channelwise(void* grouped_x, float* grouped_x_scale, float* route_weights, int* m_indices, int* output_index,
+                                  int* expert_start_loc, const void* recv_x, const float* recv_x_scale, const void* recv_topk_ids,
+                                  const float* recv_topk_weights, const int* num_recv_tokens_per_expert, int total_rows,
+                                  int recv_rows, int topk, int hidden, int num_experts, int topk_ids_i64, void* stream);
+int mm_deepep_gather_channelwise(void* recv_y, const void* l2_out, const void* recv_topk_ids, const float* recv_topk_weights,
+                                 const int* output_index, int recv_rows, int topk, int hidden, int topk_ids_i64,
+                                 int apply_topk_weights, void* stream);
+
 /* Measurement aid (no counterpart in the reference, whose test divides by a datasheet figure, tests/test_mega_moe_dcu.py:20-22):
  * launch a kernel that issues `iters` groups of eight dense FP8 MMAs (tcgen05 kind::f8f6f4, M128 x N256 x K32) per SM from
  * operands resident in shared memory.  *flops_out receives the floating-point operations of the launch; time it with events

@@ -1,0 +1,102 @@
+"""Full-size parity on one B200: the DSV4-Flash-shaped layer (256 experts, top-6, hidden 4096, intermediate 2048, 4096
+tokens, EP1 -- the benchmark workload).  The CPU oracle cannot run all of it in seconds, so the checks are
+  * bit-exact integer results against torch on the device: per-expert receive counts == bincount, every token->slot
+    entry unique and inside its expert's segment, segments aligned to 128 rows;
+  * size-independent properties of the outputs: doubling all route weights doubles y bit for bit, permuting the tokens
+    permutes y bit for bit, a second call reproduces the first;
+  * the oracle on a SAMPLE: all rows routed to four experts are recomputed on the CPU from the quantised inputs and
+    compared, route by route, with what the CUDA path stored in the combine buffer.
+"""
+import numpy as np
+import pytest
+import torch
+
+import moe_case as mc
+from oracle import moe_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+E, K, H, I, T = 256, 6, 4096, 2048, 4096
+
+
+def _make():
+    import megamoe
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(7)
+    l1q = torch.empty((E, I // 128, H // 128, 256, 128), dtype=torch.float8_e4m3fn, device=dev)
+    l1s = torch.empty((E, 2 * I), dtype=torch.float32, device=dev)
+    l2q = torch.empty((E, H // 256, I // 128, 256, 128), dtype=torch.float8_e4m3fn, device=dev)
+    l2s = torch.empty((E, H), dtype=torch.float32, device=dev)
+    for e0 in range(0, E, 32):
+        w1 = (torch.randn((32, 2 * I, H), generator=g, device=dev) / H ** 0.5).to(torch.bfloat16)
+        w2 = (torch.randn((32, H, I), generator=g, device=dev) / I ** 0.5).to(torch.bfloat16)
+        (a, as_), (b, bs_) = megamoe.transform_fp8_weights_for_mega_moe(w1, w2)
+        l1q[e0:e0 + 32], l1s[e0:e0 + 32], l2q[e0:e0 + 32], l2s[e0:e0 + 32] = a, as_, b, bs_
+        del w1, w2, a, b
+    x = torch.randn((T, H), generator=g, device=dev).to(torch.bfloat16)
+    logits = torch.randn((T, E), generator=g, device=dev)
+    return (l1q, l1s), (l2q, l2s), x, logits
+
+
+def test_dsv4_flash_ep1_4096_tokens():
+    if not torch.cuda.is_available():
+        pytest.fail("needs a CUDA device")
+    import megamoe
+    l1, l2, x, logits = _make()
+    sb = megamoe.get_symm_buffer_for_mega_moe(None, E, T, K, H, I)
+    megamoe.fill_inputs_from_router(sb, x, logits)
+    idx = sb.topk_idx[:T].clone(); w = sb.topk_weights[:T].clone()
+    stats = torch.zeros((E,), dtype=torch.int32, device="cuda")
+    y = torch.empty((T, H), dtype=torch.bfloat16, device="cuda")
+    megamoe.fp8_w8a8_mega_moe(y, l1, l2, sb, cumulative_local_expert_recv_stats=stats)
+    sb.check_status()
+
+    # ---- routing layout, bit-exact against torch on the device
+    counts = torch.bincount(idx.flatten(), minlength=E).to(torch.int32)
+    assert torch.equal(stats, counts)
+    off = sb.scratch_view("expert_off", (E,), torch.int32)
+    padded = (counts + 127) // 128 * 128
+    assert torch.equal(off, (torch.cumsum(padded, 0) - padded).to(torch.int32))
+    dest = sb.scratch_view("dest_row", (sb.num_max_tokens_per_rank, K), torch.int32)[:T]
+    flat = dest.flatten().long()
+    assert flat.unique().numel() == T * K
+    e_flat = idx.flatten()
+    assert bool(((flat >= off[e_flat].long()) & (flat < (off[e_flat] + counts[e_flat]).long())).all())
+    # rows of one expert are in (token, slot) order: the row index grows with the route index inside each expert
+    order = torch.argsort(e_flat * (T * K) + torch.arange(T * K, device="cuda"))
+    same = e_flat[order][1:] == e_flat[order][:-1]
+    assert bool((flat[order][1:][same] > flat[order][:-1][same]).all())
+
+    # ---- sampled oracle: every row of four experts, compared per route through the combine buffer
+    comb = sb.symm_view("combine", (K, sb.num_max_tokens_per_rank, H), torch.bfloat16)
+    xq, xs = sb.x[:T].cpu(), sb.x_sf[:T].cpu()
+    idx_c, w_c = idx.cpu(), w.cpu()
+    for e in (0, 77, 130, 255):
+        tt, kk = torch.nonzero(idx_c == e, as_tuple=True)
+        w1 = megamoe.unpack_weights_tiled(l1[0][e:e + 1], "l1", 2 * I)[0].cpu().float() * l1[1][e].cpu().view(-1, 1)
+        w2 = megamoe.unpack_weights_tiled(l2[0][e:e + 1], "l2", H)[0].cpu().float() * l2[1][e].cpu().view(-1, 1)
+        a = xq[tt].float() * xs[tt].view(-1, 1)
+        gu = a @ w1.t()
+        g_, u_ = gu[:, :I], gu[:, I:]
+        act = (g_ * torch.sigmoid(g_) * u_ * w_c[tt, kk].view(-1, 1)).to(torch.bfloat16).float()
+        s2 = (act.abs().amax(dim=1) / 448.0).clamp(min=1e-4)
+        aq = (act * (1.0 / s2).view(-1, 1)).to(torch.float8_e4m3fn).float()
+        ref = ((aq * s2.view(-1, 1)) @ w2.t()).to(torch.bfloat16)
+        got = comb[kk.cuda(), tt.cuda()].cpu()
+        mc.assert_end_to_end_close(got, ref, f"routes of expert {e}")
+
+    # ---- size-independent properties
+    y1 = y.clone()
+    megamoe.fp8_w8a8_mega_moe(y, l1, l2, sb)
+    assert torch.equal(y.view(torch.int16), y1.view(torch.int16)), "a second call differs"
+    sb.topk_weights[:T].copy_(w * 2)
+    megamoe.fp8_w8a8_mega_moe(y, l1, l2, sb)
+    assert torch.equal(y.view(torch.int16), (y1.float() * 2).to(torch.bfloat16).view(torch.int16)), "doubling the weights"
+    perm = torch.randperm(T, device="cuda", generator=torch.Generator(device="cuda").manual_seed(1))
+    sb.x[:T].copy_(sb.x[:T][perm].clone()); sb.x_sf[:T].copy_(sb.x_sf[:T][perm].clone())
+    sb.topk_idx[:T].copy_(idx[perm]); sb.topk_weights[:T].copy_(w[perm])
+    megamoe.fp8_w8a8_mega_moe(y, l1, l2, sb)
+    sb.check_status()
+    assert torch.equal(y.view(torch.int16), y1[perm].view(torch.int16)), "permuting the tokens"
+    assert not torch.isnan(y.float()).any()
+    sb.destroy()

@@ -98,3 +98,61 @@ def test_ep4_skewed():
 def test_ep8_token_list_like_the_reference_cli():
     # the reference test's explicit per-rank list, e.g. 0,133,0,... (tests/test_mega_moe_dcu.py:405-419)
     _run(8, dict(E=64, K=6, H=1024, I=512, tokens=[0, 133, 0, 64, 128, 1, 17, 96], seed=25))
+
+
+def _graph_worker(rank, world, port, cfg):
+    """CUDA-graph bucket replay across ranks: one capture per rank at the bucket size, replays with device-side token
+    counts that differ per rank and per replay, zero included (tests/test_mega_moe_dcu.py:563-715)."""
+    import torch.distributed as dist
+    import megamoe
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from deepgemm_b200 import _lib
+        _lib.lib().mm_set_timeouts(20000, 4000)
+        E, K, H, I, bucket = cfg["E"], cfg["K"], cfg["H"], cfg["I"], cfg["bucket"]
+        full = mc.make_case(world, E, K, H, I, [bucket] * world, seed=cfg["seed"])
+        sb = megamoe.get_symm_buffer_for_mega_moe(dist.group.WORLD, E, bucket, K, H, I)
+        l1, l2 = megamoe.transform_fp8_weights_for_mega_moe(full.w1_bf16[rank].cuda(), full.w2_bf16[rank].cuda())
+        xq, xs = megamoe.cast_to_fp8_channelwise(full.x_bf16[rank].cuda())
+        sb.x[:bucket].copy_(xq); sb.x_sf[:bucket].copy_(xs)
+        sb.topk_idx[:bucket].copy_(full.idx[rank].cuda()); sb.topk_weights[:bucket].copy_(full.w[rank].cuda())
+        y = torch.zeros((bucket, H), dtype=torch.bfloat16, device="cuda")
+        flag = {"staged": dict(stages_fused_cuda_graph=True), "fused": dict(big_fused_cuda_graph=True)}[cfg["variant"]]
+        megamoe.fp8_mega_moe(y, l1, l2, sb, **flag)           # warm-up outside capture (same call on every rank)
+        torch.cuda.synchronize(); dist.barrier()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            megamoe.fp8_mega_moe(y, l1, l2, sb, **flag)
+        for counts in cfg["replays"]:
+            n = counts[rank]
+            y.fill_(7.0)
+            sb.cuda_graph_num_tokens.fill_(n)
+            torch.cuda.synchronize(); dist.barrier()
+            graph.replay()
+            torch.cuda.synchronize()
+            sb.check_status()
+            case = mc.make_case(world, E, K, H, I, [bucket] * world, seed=cfg["seed"])
+            for r in range(world):       # the oracle sees each rank's prefix
+                case.tokens[r] = counts[r]
+                for name in ("x_bf16", "x_q", "x_s", "idx", "w"):
+                    getattr(case, name)[r] = getattr(case, name)[r][:counts[r]]
+            ys, _, _ = mc.run_oracle(case)
+            mc.assert_end_to_end_close(y[:n].cpu(), ys[rank], f"rank {rank} replay {counts}")
+            assert bool((y[n:] == 7.0).all()), "rows past the device-side token count must not be written"
+        sb.destroy()
+    finally:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("variant", ["staged", "fused"])
+def test_ep2_graph_bucket_replay_with_per_rank_token_counts(variant):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    cfg = dict(E=8, K=2, H=512, I=256, bucket=96, seed=27, variant=variant, replays=[[96, 96], [40, 77], [0, 13], [96, 0]])
+    mp.spawn(_graph_worker, args=(2, _free_port(), cfg), nprocs=2, join=True)

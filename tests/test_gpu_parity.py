@@ -266,6 +266,45 @@ def test_router_topk_and_quantisation_fill_the_buffer_in_one_kernel():
     sb.destroy()
 
 
+@pytest.mark.parametrize("ids_dtype", [torch.int64, torch.int32])
+def test_deepep_layout_helpers(ids_dtype):
+    """Scatter / gather helpers of the reference's split baseline (csrc/kernels/mega_moe_baseline_hip.cu:37-127)."""
+    import megamoe
+    g = torch.Generator().manual_seed(19)
+    tokens, topk, hidden, experts = 150, 4, 256, 12
+    x = torch.randint(0, 255, (tokens, hidden), generator=g, dtype=torch.uint8).view(torch.float8_e4m3fn)
+    xs = torch.rand((tokens,), generator=g)
+    ids = torch.randint(-1, experts, (tokens, topk), generator=g)          # -1 = not routed here
+    w = torch.rand((tokens, topk), generator=g)
+    counts = torch.bincount(ids[ids >= 0].flatten(), minlength=experts).to(torch.int32)
+    rows = int(counts.sum())
+    gx, gs, rw, mi, oi = megamoe.deepep_deepgemm_preprocess_channelwise(
+        x.cuda(), xs.cuda(), ids.to(ids_dtype).cuda(), w.cuda(), counts.cuda(), rows)
+    gx, gs, rw, mi, oi = gx.cpu(), gs.cpu(), rw.cpu(), mi.cpu(), oi.cpu()
+    start = torch.cumsum(counts, 0) - counts
+    nxt = start.clone()
+    for t in range(tokens):                       # route order inside every expert
+        for s in range(topk):
+            e = int(ids[t, s])
+            if e < 0:
+                assert oi[t, s] == -1
+                continue
+            r = int(oi[t, s])
+            assert r == int(nxt[e]); nxt[e] += 1
+            assert int(mi[r]) == e and gs[r] == xs[t] and rw[r] == w[t, s]
+            assert torch.equal(gx[r].view(torch.uint8), x[t].view(torch.uint8))
+    l2_out = torch.randn((rows, hidden), generator=g).to(torch.bfloat16)
+    for apply in (False, True):
+        y = torch.empty((tokens, hidden), dtype=torch.bfloat16, device="cuda")
+        megamoe.deepep_deepgemm_postprocess_channelwise(y, l2_out.cuda(), ids.to(ids_dtype).cuda(), w.cuda(), oi.cuda(), apply)
+        ref = torch.zeros((tokens, hidden))
+        for s in range(topk):
+            m = ids[:, s] >= 0
+            v = l2_out[oi[m, s].long()].float()
+            ref[m] += v * w[m, s].view(-1, 1) if apply else v
+        assert torch.equal(y.cpu().view(torch.int16), ref.to(torch.bfloat16).view(torch.int16))
+
+
 def test_api_argument_errors():
     import megamoe
     case = mc.make_case(1, 8, 2, 512, 256, [16], seed=11)

@@ -196,44 +196,44 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     const int k_blocks = p.kdim / kBlockK;
 
     if (warp == 0) {
-        // ------------------------------------------------------------------ TMA producer
-        int stage = 0; uint32_t phase = 0;
-        bool alive = true;
-        for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
-            const int mb = tile / p.n_blocks, nb = tile - mb * p.n_blocks;
-            const int e = p.mblock_expert[mb];
-            const int a_row = mb * kBlockM;
-            // weights are stored tile by tile in the order this kernel consumes them:
-            // [expert][n block][k block][256 rows][128 B] -- one TMA box = one contiguous 32 KiB block, and the k blocks
-            // of one output tile follow each other, so each CTA streams one sequential run of HBM per tile
-            const int b_tile0 = (e * p.n_blocks + nb) * k_blocks;
-            for (int kb = 0; kb < k_blocks; ++kb) {
-                if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.timeout_ns)) { alive = false; break; }
-                if (lane == 0) {
+        // ------------------------------------------------------------------ TMA producer (one thread)
+        if (lane == 0) {
+            int stage = 0; uint32_t phase = 0;
+            bool alive = true;
+            for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
+                const int mb = tile / p.n_blocks, nb = tile - mb * p.n_blocks;
+                const int e = p.mblock_expert[mb];
+                const int a_row = mb * kBlockM;
+                // weights are stored tile by tile in the order this kernel consumes them:
+                // [expert][n block][k block][256 rows][128 B] -- one TMA box = one contiguous 32 KiB block, and the k blocks
+                // of one output tile follow each other, so each CTA streams one sequential run of HBM per tile
+                const int b_tile0 = (e * p.n_blocks + nb) * k_blocks;
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.timeout_ns)) { alive = false; break; }
                     const uint32_t a_dst = smem_base + stage * kStageBytes;
                     const uint32_t b_dst = a_dst + kABytes;
                     mbar_arrive_expect_tx(full_bar(stage), kStageBytes);
                     tma_load_2d(a_dst, &tm_a, kb * kBlockK, a_row, full_bar(stage));
                     tma_load_2d(b_dst, &tm_b, 0, (b_tile0 + kb) * kBlockN, full_bar(stage));
+                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
                 }
-                __syncwarp();
-                if (++stage == kStages) { stage = 0; phase ^= 1u; }
             }
         }
+        __syncwarp();
     } else if (warp == 1) {
-        // ------------------------------------------------------------------ MMA issuer
-        constexpr uint32_t idesc = umma_idesc_f8(kBlockM, kBlockN);
-        int stage = 0; uint32_t phase = 0;
-        int acc = 0; uint32_t acc_phase = 0;
-        bool alive = true;
-        for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
-            if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.timeout_ns)) { alive = false; break; }
-            tc_fence_after();
-            const uint32_t d_tmem = tmem_base + acc * kBlockN;
-            for (int kb = 0; kb < k_blocks; ++kb) {
-                if (!mbar_wait(full_bar(stage), phase, abort_flag, p.timeout_ns)) { alive = false; break; }
+        // ------------------------------------------------------------------ MMA issuer (one thread)
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_f8(kBlockM, kBlockN);
+            int stage = 0; uint32_t phase = 0;
+            int acc = 0; uint32_t acc_phase = 0;
+            bool alive = true;
+            for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
+                if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.timeout_ns)) { alive = false; break; }
                 tc_fence_after();
-                if (lane == 0) {
+                const uint32_t d_tmem = tmem_base + acc * kBlockN;
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!mbar_wait(full_bar(stage), phase, abort_flag, p.timeout_ns)) { alive = false; break; }
+                    tc_fence_after();
                     const uint32_t a_src = smem_base + stage * kStageBytes;
                     const uint64_t da = umma_desc_k_sw128(a_src);
                     const uint64_t db = umma_desc_k_sw128(a_src + kABytes);
@@ -244,12 +244,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                     }
                     umma_commit(empty_bar(stage));            // smem stage is free once these MMAs retire
                     if (kb == k_blocks - 1) umma_commit(tfull_bar(acc));   // accumulator complete
+                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
                 }
-                __syncwarp();
-                if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
             }
-            if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
         }
+        __syncwarp();
     } else {
         // ------------------------------------------------------------------ epilogue (warps 2..9)
         // Two warps per TMEM lane quarter: warp 2+q (half 0) and warp 6+q (half 1) split the tile's columns, so every

@@ -188,6 +188,81 @@ def run_reference_arm(args):
     }))
 
 
+def run_sweep(args):
+    """--sweep: the scaling sweep of the layer (tokens per rank x routing skew) at the launched EP size.  One JSON line per
+    point from rank 0: tokens/s, FP8 TFLOP/s, NVLink GB/s per rank and the three roofline times (tensor at the measured FP8
+    peak, HBM at the measured copy peak, NVLink at the measured 770 GB/s per direction); max over ranks, CUDA events."""
+    dist, group, rank, world, local = init_dist(args.gpus)
+    dev = torch.device("cuda", local)
+    import megamoe
+    from deepgemm_b200 import _lib
+    token_list = [int(t) for t in args.sweep.split(",")]
+    t_max = max(token_list)
+    e_loc = E // world
+    l1, l2, _, _, _ = make_rank_data(rank, world, 8, dev)
+    sb = megamoe.get_symm_buffer_for_mega_moe(group, E, t_max, K, H, I)
+    fp8_peak = _lib.fp8_mma_peak_tflops()
+    hbm_peak, _ = measured_peaks()
+    g = torch.Generator(device=dev).manual_seed(2000 + rank)
+    gp = torch.Generator().manual_seed(12345)
+    pop = torch.empty(E)
+    pop[torch.randperm(E, generator=gp)] = torch.arange(1, E + 1, dtype=torch.float32) ** -1.1
+    log_pop = torch.log(pop / pop.sum()).to(dev)
+    for routing in ("uniform", "zipf"):
+        for T in token_list:
+            x = torch.randn((T, H), generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+            logits = torch.randn((T, E), generator=g, device=dev, dtype=torch.float32)
+            if routing == "zipf":
+                logits = logits + 1.5 * log_pop.view(1, -1)
+            megamoe.fill_inputs_from_router(sb, x, logits)
+            y = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
+            stats = torch.zeros((e_loc,), dtype=torch.int32, device=dev)
+            megamoe.fp8_w8a8_mega_moe(y, l1, l2, sb, cumulative_local_expert_recv_stats=stats)
+            for _ in range(3):
+                megamoe.fp8_w8a8_mega_moe(y, l1, l2, sb)
+            torch.cuda.synchronize()
+            if dist is not None:
+                dist.barrier(group)
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            steps = max(5, args.steps)
+            ev0.record()
+            for _ in range(steps):
+                megamoe.fp8_w8a8_mega_moe(y, l1, l2, sb)
+            ev1.record()
+            torch.cuda.synchronize()
+            sb.check_status()
+            ms = ev0.elapsed_time(ev1) / steps
+            rows = int(stats.sum().item()); touched = int((stats > 0).sum().item())
+            vals = torch.tensor([ms, rows, touched, float(stats.max().item())], dtype=torch.float64, device=dev)
+            if dist is not None:
+                allv = [torch.zeros_like(vals) for _ in range(world)]
+                dist.all_gather(allv, vals)
+                allv = torch.stack(allv)
+            else:
+                allv = vals.view(1, -1)
+            ms = float(allv[:, 0].max()); rows_max = float(allv[:, 1].max()); rows_sum = float(allv[:, 1].sum())
+            t_tensor = rows_max * FLOP_PER_ROW / (fp8_peak * 1e12) * 1e3
+            hbm_bytes = float(allv[:, 2].max()) * (3 * H * I + 4 * (2 * I + H)) + rows_max * (H + 4 + (I + 4) * 2 + 2 * H)
+            t_hbm = hbm_bytes / (hbm_peak * 1e9) * 1e3
+            remote = rows_max * (world - 1) / world
+            t_nvl = remote * (H + 16 + 2 * H) / 770e9 * 1e3          # dispatch in + combine out share a direction in time
+            t_roof = max(t_tensor, t_hbm, t_nvl)
+            if rank == 0:
+                print(json.dumps({
+                    "sweep": True, "ep": world, "tokens_per_rank": T, "routing": routing, "ms": round(ms, 4),
+                    "tokens_per_s": round(T * world / (ms * 1e-3)), "fp8_tflops_total": round(rows_sum * FLOP_PER_ROW / (ms * 1e-3) / 1e12, 1),
+                    "fp8_frac_of_measured_peak_per_gpu": round(rows_max * FLOP_PER_ROW / (ms * 1e-3) / 1e12 / fp8_peak, 3),
+                    "nvlink_gbs_per_rank": round(remote * (H + 16 + 2 * H) / (ms * 1e-3) / 1e9, 1),
+                    "max_rows_per_expert": int(allv[:, 3].max()), "rows_max_rank": int(rows_max),
+                    "roof_ms": {"tensor": round(t_tensor, 4), "hbm": round(t_hbm, 4), "nvlink": round(t_nvl, 4)},
+                    "frac_of_roofline": round(t_roof / ms, 3),
+                    "variant": "fused" if (T <= sb._large_opt_3stage_threshold and T * K <= 4096) else "staged"}), flush=True)
+    sb.destroy()
+    if dist is not None:
+        dist.barrier(group)
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -199,10 +274,14 @@ def main():
     ap.add_argument("--experts", type=int, default=E, help="total experts (reduce only for small profiler captures)")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--sweep", default=None, help="comma-separated tokens-per-rank list: run the scaling sweep instead of the bench")
     args = ap.parse_args()
     globals()["E"] = args.experts
     if args.impl == "reference":
         run_reference_arm(args)
+        return
+    if args.sweep:
+        run_sweep(args)
         return
 
     dist, group, rank, world, local = init_dist(args.gpus)

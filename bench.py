@@ -201,7 +201,8 @@ def run_sweep(args):
     e_loc = E // world
     l1, l2, _, _, _ = make_rank_data(rank, world, 8, dev)
     sb = megamoe.get_symm_buffer_for_mega_moe(group, E, t_max, K, H, I)
-    fp8_peak = _lib.fp8_mma_peak_tflops()
+    fp8_peak = _lib.fp8_mma_peak_tflops()                                   # all-ones operands: the burst rate
+    fp8_peak_data = _lib.fp8_mma_peak_tflops(random_operands=True)          # random operands: what real data can reach
     hbm_peak, _ = measured_peaks()
     g = torch.Generator(device=dev).manual_seed(2000 + rank)
     gp = torch.Generator().manual_seed(12345)
@@ -217,9 +218,9 @@ def run_sweep(args):
             megamoe.fill_inputs_from_router(sb, x, logits)
             y = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
             stats = torch.zeros((e_loc,), dtype=torch.int32, device=dev)
-            megamoe.fp8_w8a8_mega_moe(y, l1, l2, sb, cumulative_local_expert_recv_stats=stats)
+            megamoe.fp8_w8a8_mega_moe(y, l1, l2, sb, cumulative_local_expert_recv_stats=stats, dispatch_num_tokens=T)
             for _ in range(3):
-                megamoe.fp8_w8a8_mega_moe(y, l1, l2, sb)
+                megamoe.fp8_w8a8_mega_moe(y, l1, l2, sb, dispatch_num_tokens=T)
             torch.cuda.synchronize()
             if dist is not None:
                 dist.barrier(group)
@@ -227,7 +228,7 @@ def run_sweep(args):
             steps = max(5, args.steps)
             ev0.record()
             for _ in range(steps):
-                megamoe.fp8_w8a8_mega_moe(y, l1, l2, sb)
+                megamoe.fp8_w8a8_mega_moe(y, l1, l2, sb, dispatch_num_tokens=T)   # every rank holds T tokens
             ev1.record()
             torch.cuda.synchronize()
             sb.check_status()
@@ -241,7 +242,7 @@ def run_sweep(args):
             else:
                 allv = vals.view(1, -1)
             ms = float(allv[:, 0].max()); rows_max = float(allv[:, 1].max()); rows_sum = float(allv[:, 1].sum())
-            t_tensor = rows_max * FLOP_PER_ROW / (fp8_peak * 1e12) * 1e3
+            t_tensor = rows_max * FLOP_PER_ROW / (fp8_peak_data * 1e12) * 1e3   # against the rate random operands reach
             hbm_bytes = float(allv[:, 2].max()) * (3 * H * I + 4 * (2 * I + H)) + rows_max * (H + 4 + (I + 4) * 2 + 2 * H)
             t_hbm = hbm_bytes / (hbm_peak * 1e9) * 1e3
             remote = rows_max * (world - 1) / world
@@ -251,7 +252,8 @@ def run_sweep(args):
                 print(json.dumps({
                     "sweep": True, "ep": world, "tokens_per_rank": T, "routing": routing, "ms": round(ms, 4),
                     "tokens_per_s": round(T * world / (ms * 1e-3)), "fp8_tflops_total": round(rows_sum * FLOP_PER_ROW / (ms * 1e-3) / 1e12, 1),
-                    "fp8_frac_of_measured_peak_per_gpu": round(rows_max * FLOP_PER_ROW / (ms * 1e-3) / 1e12 / fp8_peak, 3),
+                    "fp8_frac_of_measured_peak_per_gpu": round(rows_max * FLOP_PER_ROW / (ms * 1e-3) / 1e12 / fp8_peak_data, 3),
+                    "fp8_peak_tflops": {"ones_operands": round(fp8_peak, 1), "random_operands": round(fp8_peak_data, 1)},
                     "nvlink_gbs_per_rank": round(remote * (H + 16 + 2 * H) / (ms * 1e-3) / 1e9, 1),
                     "max_rows_per_expert": int(allv[:, 3].max()), "rows_max_rank": int(rows_max),
                     "roof_ms": {"tensor": round(t_tensor, 4), "hbm": round(t_hbm, 4), "nvlink": round(t_nvl, 4)},

@@ -37,7 +37,7 @@ _SIGNATURES = {
     "mm_quant_per_token": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p]),
     "mm_deepep_scatter_channelwise": (c_int, [c_void_p] * 11 + [c_int] * 6 + [c_void_p]),
     "mm_deepep_gather_channelwise": (c_int, [c_void_p] * 5 + [c_int] * 5 + [c_void_p]),
-    "mm_fp8_mma_peak_probe": (c_int, [c_int, c_void_p, c_void_p, POINTER(ctypes.c_double)]),
+    "mm_fp8_mma_peak_probe": (c_int, [c_int, c_int, c_int, c_void_p, c_void_p, POINTER(ctypes.c_double)]),
     "mm_router_topk_quant": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "mm_fp8_w8a8_mega_moe": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                      POINTER(c_uint64), c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
@@ -112,8 +112,9 @@ def stage_times() -> dict:
     return {n: float(v) for n, v in zip(STAGE_NAMES, buf) if v >= 0}
 
 
-def fp8_mma_peak_tflops(iters: int = 20000, repeats: int = 5) -> float:
-    """Dense FP8 tensor-core rate (TFLOP/s) measured with the library's probe kernel on the current device (best of repeats)."""
+def fp8_mma_peak_tflops(iters: int = 20000, repeats: int = 5, random_operands: bool = False, cta_pair: bool = False) -> float:
+    """Dense FP8 tensor-core rate (TFLOP/s) measured with the library's probe kernel on the current device (best of repeats).
+    random_operands: pseudo-random e4m3 data instead of all ones (draws more power, so the clock and the rate are lower)."""
     import torch
     status = torch.zeros((1,), dtype=torch.int32, device="cuda")
     stream = torch.cuda.current_stream().cuda_stream
@@ -122,7 +123,7 @@ def fp8_mma_peak_tflops(iters: int = 20000, repeats: int = 5) -> float:
     for _ in range(repeats + 1):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        check(lib().mm_fp8_mma_peak_probe(iters, status.data_ptr(), stream, ctypes.byref(flops)))
+        check(lib().mm_fp8_mma_peak_probe(iters, int(random_operands), int(cta_pair), status.data_ptr(), stream, ctypes.byref(flops)))
         e1.record()
         torch.cuda.synchronize()
         best = max(best, flops.value / (e0.elapsed_time(e1) * 1e-3) / 1e12)

@@ -15,6 +15,7 @@
 #include "deepep_layout.cuh"
 #include "fused.cuh"
 #include "gemm.cuh"
+#include "gemm_pair.cuh"
 #include "layout.h"
 #include "misc.cuh"
 #include "probe.cuh"
@@ -134,7 +135,39 @@ int ensure_gemm_attrs() {
     MM_CUDA(cudaFuncSetAttribute(mm::grouped_gemm_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, mm::kGemmSmemBytes));
     MM_CUDA(cudaFuncSetAttribute(mm::grouped_gemm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, mm::kGemmSmemBytes));
     MM_CUDA(cudaFuncSetAttribute(mm::mega_moe_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, mm::kGemmSmemBytes));
+    MM_CUDA(cudaFuncSetAttribute(mm::grouped_gemm_pair_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, mm::kPairSmemBytes));
+    MM_CUDA(cudaFuncSetAttribute(mm::grouped_gemm_pair_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, mm::kPairSmemBytes));
     if (dev < 64) done[dev] = true;
+    return 0;
+}
+
+// CTA pairs that can be resident at once (the pair kernels stride their tiles over the grid, so a pair that only
+// starts after another has finished would double the run time).  Not every SM need have a free partner in its GPC.
+int pair_cluster_count(int sms, int* out) {
+    static std::mutex mu;
+    static int cached[64] = {0};
+    int dev = 0;
+    MM_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lk(mu);
+    if (dev < 64 && cached[dev]) { *out = cached[dev] > 0 ? cached[dev] : 0; return 0; }
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(sms / 2 * 2);
+    cfg.blockDim = dim3(mm::kGemmThreads);
+    cfg.dynamicSmemBytes = mm::kPairSmemBytes;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int n0 = 0, n1 = 0;
+    MM_CUDA(cudaOccupancyMaxActiveClusters(&n0, mm::grouped_gemm_pair_kernel<0>, &cfg));
+    MM_CUDA(cudaOccupancyMaxActiveClusters(&n1, mm::grouped_gemm_pair_kernel<1>, &cfg));
+    int n = n0 < n1 ? n0 : n1;
+    if (n > sms / 2) n = sms / 2;
+    if (dev < 64) cached[dev] = n > 0 ? n : -1;
+    if (getenv("MEGAMOE_VERBOSE")) fprintf(stderr, "megamoe: %d resident CTA pairs on %d SMs (device %d)\n", n, sms, dev);
+    *out = n;
     return 0;
 }
 
@@ -334,8 +367,9 @@ int mm_deepep_gather_channelwise(void* recv_y, const void* l2_out, const void* r
     return 0;
 }
 
-int mm_fp8_mma_peak_probe(int iters, int* status_dev, void* stream_, double* flops_out) {
-    MM_REQUIRE(iters > 0 && status_dev, "mm_fp8_mma_peak_probe: bad arguments");
+int mm_fp8_mma_peak_probe(int iters, int operands, int cta_pair, int* status_dev, void* stream_, double* flops_out) {
+    MM_REQUIRE(iters > 0 && status_dev && (operands == 0 || operands == 1) && (cta_pair == 0 || cta_pair == 1),
+               "mm_fp8_mma_peak_probe: bad arguments");
     int sms = 0;
     if (int rc = sm_count(&sms)) return rc;
     static bool attr_done = false;
@@ -343,7 +377,14 @@ int mm_fp8_mma_peak_probe(int iters, int* status_dev, void* stream_, double* flo
         MM_CUDA(cudaFuncSetAttribute(mm::fp8_mma_peak_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, mm::kABytes + mm::kBBytes));
         attr_done = true;
     }
-    mm::fp8_mma_peak_kernel<<<sms, 128, mm::kABytes + mm::kBBytes, static_cast<cudaStream_t>(stream_)>>>(iters, status_dev);
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (cta_pair) {
+        sms = sms / 2 * 2;
+        MM_CUDA(cudaFuncSetAttribute(mm::fp8_mma_peak_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, mm::kABytes + mm::kBBytes));
+        mm::fp8_mma_peak_pair_kernel<<<sms, 128, mm::kABytes + mm::kBBytes, stream>>>(iters, status_dev, operands);
+    } else {
+        mm::fp8_mma_peak_kernel<<<sms, 128, mm::kABytes + mm::kBBytes, stream>>>(iters, status_dev, operands);
+    }
     MM_LAUNCHED();
     if (flops_out) *flops_out = (double)sms * iters * 8.0 * 2.0 * mm::kBlockM * mm::kBlockN * 32.0;
     return 0;
@@ -417,6 +458,9 @@ int mm_fp8_w8a8_mega_moe(void* y, const void* w1, const float* s1, const void* w
     g1.plan = reinterpret_cast<const int*>(sc + rp.cl.plan);
     g1.mblock_expert = reinterpret_cast<const int*>(sc + rp.cl.mblock_expert);
     g1.mblock_valid = reinterpret_cast<const int*>(sc + rp.cl.mblock_valid);
+    g1.expert_total = reinterpret_cast<const int*>(sc + rp.cl.expert_total);
+    g1.expert_off = reinterpret_cast<const int*>(sc + rp.cl.expert_off);
+    g1.E_loc = E_loc;
     g1.meta = reinterpret_cast<const MmPoolMeta*>(rp.sym + rp.sl.pool_meta);
     g1.status = reinterpret_cast<int*>(sc + rp.cl.status);
     g1.timeout_ns = (uint64_t)g_pipe_ms.load() * 1000000ull;
@@ -484,12 +528,30 @@ int mm_fp8_w8a8_mega_moe(void* y, const void* w1, const float* s1, const void* w
         MM_STAGE(MM_STAGE_FUSED);
         return 0;
     }
-    mm::grouped_gemm_kernel<0><<<sms, mm::kGemmThreads, mm::kGemmSmemBytes, stream>>>(tm_pool, tm_w1, g1);
+    // CTA-pair GEMMs (two m-blocks of one expert share each weight tile) once an expert can expect two full m-blocks;
+    // MEGAMOE_GEMM_PAIR=0/1 overrides the choice (tests run both kernels on the same inputs).
+    bool pair_gemms = (int64_t)R * tokens_bound * K >= (int64_t)E_loc * 2 * MM_BLOCK_M && sms >= 2;
+    if (const char* v = getenv("MEGAMOE_GEMM_PAIR")) pair_gemms = v[0] == '1' && sms >= 2;
+    CUtensorMap tm_w1h, tm_w2h;
+    if (pair_gemms) {
+        if (int rc = tensor_map_2d(w1, 128, (uint64_t)E_loc * (I / 128) * (H / 128) * 256, 128, &tm_w1h)) return rc;
+        if (int rc = tensor_map_2d(w2, 128, (uint64_t)E_loc * ((H + 255) / 256) * (I / 128) * 256, 128, &tm_w2h)) return rc;
+    }
+    int pair_grid = 0;
+    if (pair_gemms) {
+        int clusters = 0;
+        if (int rc = pair_cluster_count(sms, &clusters)) return rc;
+        if (clusters < sms / 4) pair_gemms = false;      // too few resident pairs to be worth it
+        pair_grid = 2 * clusters;
+    }
+    if (pair_gemms) mm::grouped_gemm_pair_kernel<0><<<pair_grid, mm::kGemmThreads, mm::kPairSmemBytes, stream>>>(tm_pool, tm_w1h, g1);
+    else mm::grouped_gemm_kernel<0><<<sms, mm::kGemmThreads, mm::kGemmSmemBytes, stream>>>(tm_pool, tm_w1, g1);
     MM_STAGE(MM_STAGE_GEMM1);
     mm::requant_kernel<<<sms * 4, 256, 0, stream>>>(g1.act_bf16, I, g1.plan, g1.mblock_valid, g1.row_amax,
                                                    reinterpret_cast<float*>(sc + rp.cl.act_scale), sc + rp.cl.act_fp8);
     MM_STAGE(MM_STAGE_REQUANT);
-    mm::grouped_gemm_kernel<1><<<sms, mm::kGemmThreads, mm::kGemmSmemBytes, stream>>>(tm_act, tm_w2, g2);
+    if (pair_gemms) mm::grouped_gemm_pair_kernel<1><<<pair_grid, mm::kGemmThreads, mm::kPairSmemBytes, stream>>>(tm_act, tm_w2h, g2);
+    else mm::grouped_gemm_kernel<1><<<sms, mm::kGemmThreads, mm::kGemmSmemBytes, stream>>>(tm_act, tm_w2, g2);
     MM_STAGE(MM_STAGE_GEMM2);
     if (R > 1) {
         mm::rank_barrier_kernel<<<1, 32, 0, stream>>>(rp, MM_BAR_COMBINE);

@@ -38,7 +38,10 @@ struct GemmParams {
     int n_blocks;              // tiles along the weight rows (I/128 for kind 0, ceil(H/256) for kind 1)
     int n_out;                 // I (kind 0) or H (kind 1): valid output columns
     int w_rows_per_expert;     // 2I (kind 0) or H (kind 1)
-    const int* plan;           // [0] = number of m-blocks in use
+    const int* plan;           // [0] = number of m-blocks in use, [2] = number of m-block pairs (gemm_pair.cuh)
+    const int* expert_total;   // [E_loc] rows received per local expert
+    const int* expert_off;     // [E_loc] first pool row of each local expert
+    int E_loc;
     const int* mblock_expert;
     const int* mblock_valid;
     const MmPoolMeta* meta;    // per pool row

@@ -160,16 +160,19 @@ __global__ void __launch_bounds__(1024) route_plan_kernel(RouteParams p) {
     }
     __syncthreads();
     if (threadIdx.x < p.R) {   // one thread per owner: exclusive prefix of padded totals over its experts
-        int run = 0;
+        int run = 0, pairs = 0;
         for (int le = 0; le < p.E_loc; ++le) {
             const int e = threadIdx.x * p.E_loc + le;
             off[e] = run;
-            run += (tot[e] + MM_BLOCK_M - 1) / MM_BLOCK_M * MM_BLOCK_M;
+            const int blocks = (tot[e] + MM_BLOCK_M - 1) / MM_BLOCK_M;
+            run += blocks * MM_BLOCK_M;
+            pairs += (blocks + 1) / 2;      // two m-blocks of one expert share a weight tile in the CTA-pair GEMMs
         }
         if (threadIdx.x == p.rank) {
             int* plan = reinterpret_cast<int*>(p.scratch + p.cl.plan);
             plan[0] = run / MM_BLOCK_M;
             plan[1] = run;
+            plan[2] = pairs;
             if (run > p.sl.pool_rows) report_status(p.scratch, p.cl, MM_ERR_POOL_OVERFLOW, 0, p.rank, (int)p.sl.pool_rows, run);
         }
     }

@@ -75,6 +75,21 @@ def _large_opt_3stage_selected(num_tokens: int, mode: str, threshold: int) -> bo
     return False
 
 
+def _eager_variant_is_staged(num_ranks: int, mode: str, threshold: int, y_tokens: int, dispatch_num_tokens: Optional[int],
+                             capacity: int, topk: int) -> bool:
+    """Variant of an eager (non-graph) call.  Every rank of a group must run the same variant (the staged launches and
+    the fused kernel signal one another differently), while ranks may hold different token counts
+    (tests/test_mega_moe_dcu.py:405-419 passes per-rank lists).  So with more than one rank the choice is made on what
+    all ranks share: the caller's dispatch_num_tokens if given, else the buffer's capacity per rank."""
+    tokens = y_tokens if dispatch_num_tokens is None else int(dispatch_num_tokens)
+    if num_ranks > 1 and dispatch_num_tokens is None:
+        tokens = capacity
+    staged = _large_opt_3stage_selected(tokens, mode, threshold)
+    if not staged and mode != "off" and tokens * topk > _FUSED_MAX_ROUTES:
+        staged = True          # beyond the fused kernel's shared-memory routing capacity
+    return staged
+
+
 def _is_current_stream_capturing() -> bool:
     checker = getattr(torch.cuda, "is_current_stream_capturing", None)
     return bool(checker()) if checker is not None else False
@@ -449,11 +464,16 @@ def fp8_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer: SymmBuffer
         dispatch_tokens = int(y.size(0)) if dispatch_num_tokens is None else int(dispatch_num_tokens)
         if dispatch_tokens < 0 or dispatch_tokens > int(sb.num_max_tokens_per_rank):
             raise ValueError(f"dispatch_num_tokens must be in 0..{int(sb.num_max_tokens_per_rank)}")
-        staged = _large_opt_3stage_selected(dispatch_tokens, sb._large_opt_3stage_mode, sb._large_opt_3stage_threshold)
+        staged = _eager_variant_is_staged(sb.num_ranks, sb._large_opt_3stage_mode, sb._large_opt_3stage_threshold,
+                                          int(y.size(0)), dispatch_num_tokens, int(sb.num_max_tokens_per_rank), sb.num_topk)
         call_y = y
         runtime_ptr = None
     if not staged and not graph_mode and int(call_y.size(0)) * sb.num_topk > _FUSED_MAX_ROUTES:
-        staged = True      # beyond the fused kernel's shared-memory routing capacity (same rule on every rank: uniform shapes)
+        if sb.num_ranks > 1:
+            raise RuntimeError(f"the fused variant holds at most {_FUSED_MAX_ROUTES} routes (tokens x top-k) per rank; "
+                               "let every rank take the staged variant (MEGAMOE_DCU_USE_LARGE_OPT_3STAGE=1 or a larger "
+                               "dispatch_num_tokens)")
+        staged = True
 
     # argument checks of csrc/apis/mega_dcu.hpp:355-445
     if tuple(recipe) != (1, 1, 32):

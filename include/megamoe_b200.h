@@ -151,10 +151,14 @@ int mm_deepep_gather_channelwise(void* recv_y, const void* l2_out, const void* r
                                  int apply_topk_weights, void* stream);
 
 /* Measurement aid (no counterpart in the reference, whose test divides by a datasheet figure, tests/test_mega_moe_dcu.py:20-22):
- * launch a kernel that issues `iters` groups of eight dense FP8 MMAs (tcgen05 kind::f8f6f4, M128 x N256 x K32) per SM from
+ * launch a kernel that issues `iters` groups of eight dense FP8 MMAs (tcgen05 kind::f8f6f4, M128 x N256 x K32 per SM) from
  * operands resident in shared memory.  *flops_out receives the floating-point operations of the launch; time it with events
- * on `stream` to get the tensor-core rate the GEMM kernels can at best reach.  status_dev: a zeroed device int. */
-int mm_fp8_mma_peak_probe(int iters, int* status_dev, void* stream, double* flops_out);
+ * on `stream` to get the tensor-core rate the GEMM kernels can at best reach.
+ *   operands: 0 = every byte 1.0 (few bits toggle: the burst rate), 1 = pseudo-random finite e4m3 values of both signs
+ *             (the power draw of real data; under the board's power cap the sustained rate is lower and falls over seconds);
+ *   cta_pair: 0 = cta_group::1 MMAs, 1 = cta_group::2 MMAs (M256 over two SMs) as the CTA-pair GEMM kernels issue them.
+ * status_dev: a zeroed device int. */
+int mm_fp8_mma_peak_probe(int iters, int operands, int cta_pair, int* status_dev, void* stream, double* flops_out);
 
 /* Per-stage device timing of the layer call (the reference's test prints per-kernel times with a profiler,
  * tests/test_mega_moe_dcu.py:794-834; here CUDA events are recorded on the caller's stream around every launch).

@@ -185,6 +185,25 @@ def test_skewed_routing_many_blocks_per_expert():
     _check_case(mc.make_case(1, 16, 4, 512, 256, [1500], seed=5, zipf=True))
 
 
+@pytest.mark.parametrize("shape", [
+    (8, 2, 512, 256, 700, False),      # one to two m-blocks per expert: pairs with and without a second half
+    (16, 4, 512, 256, 1500, True),     # skewed: long runs of pairs for hot experts, experts without rows
+    (4, 4, 384, 384, 70, False),       # one partial m-block per expert, hidden not a multiple of 256
+    (16, 6, 4096, 2048, 512, False),   # flagship tile shapes
+])
+def test_cta_pair_gemms_match_the_single_cta_kernels(shape, monkeypatch):
+    """The CTA-pair GEMMs (two m-blocks of one expert per weight tile, tcgen05 cta_group::2) run the same MMAs in the
+    same K order and the same epilogue as the one-CTA kernels: outputs agree bit for bit, and with the oracle."""
+    E, K, H, I, T, zipf = shape
+    case = mc.make_case(1, E, K, H, I, [T], seed=21, zipf=zipf, invalid_fraction=0.05)
+    monkeypatch.setenv("MEGAMOE_GEMM_PAIR", "0")
+    a, _ = mc.run_cuda_rank(case, 0, variant="staged", clamp=10.0)
+    monkeypatch.setenv("MEGAMOE_GEMM_PAIR", "1")
+    b, _ = mc.run_cuda_rank(case, 0, variant="staged", clamp=10.0)
+    assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+    _check_case(case, clamp=10.0, variant="staged")
+
+
 def test_marlin_weights_and_stats_accumulate():
     import megamoe
     case = mc.make_case(1, 8, 2, 512, 256, [128], seed=6)

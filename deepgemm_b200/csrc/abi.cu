@@ -528,9 +528,10 @@ int mm_fp8_w8a8_mega_moe(void* y, const void* w1, const float* s1, const void* w
         MM_STAGE(MM_STAGE_FUSED);
         return 0;
     }
-    // CTA-pair GEMMs (two m-blocks of one expert share each weight tile) once an expert can expect two full m-blocks;
-    // MEGAMOE_GEMM_PAIR=0/1 overrides the choice (tests run both kernels on the same inputs).
-    bool pair_gemms = (int64_t)R * tokens_bound * K >= (int64_t)E_loc * 2 * MM_BLOCK_M && sms >= 2;
+    // CTA-pair GEMMs (two m-blocks of one expert share each weight tile): opt-in with MEGAMOE_GEMM_PAIR=1.  Measured on
+    // B200 they tie with the one-CTA kernels at 1536 rows per expert and lose about 9 % on GEMM1 at 768 rows per expert
+    // (EP8, 4096 tokens per rank), where a third pair of an expert is often half empty.
+    bool pair_gemms = false;
     if (const char* v = getenv("MEGAMOE_GEMM_PAIR")) pair_gemms = v[0] == '1' && sms >= 2;
     CUtensorMap tm_w1h, tm_w2h;
     if (pair_gemms) {

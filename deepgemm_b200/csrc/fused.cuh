@@ -7,15 +7,19 @@
 //   2. wait (bounded) for all ranks' count vectors, derive the plan (totals, pool offsets, m-block table) locally;
 //   3. push this CTA's share of the routed rows to the owners' pools over NVLink; every row bumps the owner's per-m-block
 //      arrival counter (red.release.sys);
-//   4. tile loop over [all GEMM1 tiles, then all GEMM2 tiles], round-robin over CTAs, with the same TMA / MMA / epilogue
-//      warp roles as grouped_gemm_kernel.  Dependencies are per m-block, not global barriers:
-//        - GEMM1 tile: weights start streaming at once; the token operand waits for the m-block's arrival counter;
-//        - the CTA that finishes the last GEMM1 tile of an m-block requantises its rows with all epilogue warps (the
-//          channelwise scale needs the whole row) and sets l2_ready[m-block];
+//   4. tile loop, round-robin over CTAs, with the same TMA / MMA / epilogue warp roles as grouped_gemm_kernel.  The
+//      m-blocks are grouped in waves; GEMM1 tiles of wave k+2, requantisation tiles of wave k and GEMM2 tiles of wave k
+//      alternate (see WaveOrder), so the tensor-bound GEMM1 work overlaps the NVLink-bound combine stores of GEMM2.
+//      Dependencies are per m-block, not global barriers:
+//        - GEMM1 tile: weights start streaming at once; the token operand waits for the m-block's arrival counter; each
+//          epilogue warp counts its stored share in l1_done[m-block];
+//        - requantisation tile (epilogue warps only, the MMA pipeline runs on): waits for all GEMM1 tiles of the m-block,
+//          turns its bf16 rows into e4m3 (the channelwise scale needs the whole row) and sets l2_ready[m-block];
 //        - GEMM2 tile: the activation operand waits for l2_ready[m-block] == 4; its epilogue stores to the source rank;
 //   5. grid barrier -> CTA 0 tells every rank "my combine stores are done"; wait for all ranks; top-k reduce; clean up.
-// Because every CTA issues all of its GEMM1 tiles before its first GEMM2 tile, and GEMM1 tiles depend only on dispatch,
-// the waits cannot form a cycle.  Every wait is bounded and ends in a status code, never in a hang.
+// Every wait is for tiles earlier in the tile order (or for dispatch), and every role of a CTA walks its tiles in order,
+// so the waits cannot form a cycle.  Every wait is bounded and ends in a status code, never in a hang.
+// gemm_only = 1 starts at step 4 after the staged routing / dispatch launches (any token count).
 #pragma once
 #include "gemm.cuh"
 #include "misc.cuh"
@@ -66,6 +70,35 @@ __device__ __forceinline__ bool wait_flag_ge(const int* flag, int target, bool s
         __nanosleep(40);
     }
 }
+
+// Position of a tile index in the wave order of the kernel below.  A CTA's tile indices grow, so seek() only moves forward.
+struct WaveOrder {
+    enum { kG1 = 0, kRequant = 1, kG2 = 2 };
+    int n_waves, wave_m, num_mblocks, nb1, nb2;
+    int g, base, size, kind, wave;
+    __device__ WaveOrder(int num_mblocks_, int wave_m_, int nb1_, int nb2_)
+        : n_waves((num_mblocks_ + wave_m_ - 1) / wave_m_), wave_m(wave_m_), num_mblocks(num_mblocks_), nb1(nb1_), nb2(nb2_),
+          g(0), base(0) { set(); }
+    __device__ __forceinline__ int wave_mblocks(int w) const { return w < n_waves ? min(wave_m, num_mblocks - w * wave_m) : 0; }
+    __device__ __forceinline__ void set() {      // groups: G1(0), G1(1), then triples R(k), G1(k+2), G2(k)
+        if (g < 2) { kind = kG1; wave = g; }
+        else {
+            const int k = (g - 2) / 3, j = (g - 2) - 3 * k;
+            kind = j == 0 ? kRequant : (j == 1 ? kG1 : kG2);
+            wave = j == 1 ? k + 2 : k;
+        }
+        size = wave_mblocks(wave) * (kind == kG1 ? nb1 : (kind == kRequant ? 1 : nb2));
+    }
+    // tile -> (kind, m-block, n-block); the caller guarantees tile < num_mblocks * (nb1 + 1 + nb2)
+    __device__ __forceinline__ void seek(int tile, int& kind_out, int& mb, int& nb) {
+        while (tile >= base + size) { base += size; ++g; set(); }
+        const int r = tile - base;
+        const int per = kind == kG1 ? nb1 : (kind == kRequant ? 1 : nb2);
+        mb = wave * wave_m + r / per;
+        nb = r - (r / per) * per;
+        kind_out = kind;
+    }
+};
 
 __global__ void __launch_bounds__(kFusedThreads, 1)
 mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_constant__ CUtensorMap tm_w1,
@@ -294,42 +327,83 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
     // ------------------------------------------------------------------ phase 4: GEMM1 tiles, then GEMM2 tiles
     const GemmParams& g1 = fp.g1;
     const GemmParams& g2 = fp.g2;
-    // Tile order: m-blocks are grouped in waves of `wave_mblocks`; the global order is
-    //     G1(0), G1(1), G2(0), G1(2), G2(1), ..., G1(n-1), G2(n-2), G2(n-1)
-    // (G1(k) / G2(k) = all GEMM1 / GEMM2 tiles of wave k).  Interleaving the two GEMMs spreads the combine stores (NVLink)
-    // over the whole compute phase; putting G2(k) after G1(k+1) gives the requantisation of wave k a full wave of slack.
-    // A GEMM2 tile only ever waits for GEMM1 tiles that come earlier in this order, so the waits cannot form a cycle.
+    // Tile order: m-blocks are grouped in waves of `wave_mblocks`; with G1(k) / G2(k) = all GEMM1 / GEMM2 tiles of wave k
+    // and R(k) = one requantisation tile per m-block of wave k (epilogue warps only), the global order is
+    //     G1(0), G1(1), [R(0), G1(2), G2(0)], [R(1), G1(3), G2(1)], ..., [R(n-1), G2(n-1)]
+    // Interleaving the two GEMMs spreads the combine stores (NVLink) over the whole compute phase; R(k) comes a full
+    // wave after G1(k) and G2(k) a full wave after R(k), so their waits are normally satisfied on arrival.
+    // Every wait is for tiles that come earlier in this order and every role of a CTA walks its tiles in order, so the
+    // waits cannot form a cycle.
     const int nb1 = g1.n_blocks, nb2 = g2.n_blocks;
-    const int wave_m = max(1, fp.wave_mblocks);
-    const int n_waves = (num_mblocks + wave_m - 1) / wave_m;
-    auto decode_tile = [&](int tile, bool& second, int& mb, int& nb) {
-        const int A = wave_m * nb1, B = wave_m * nb2;                       // tiles of a full wave
-        const int last_m = num_mblocks - (n_waves - 1) * wave_m;            // m-blocks of the last wave
-        int wave, r;
-        if (n_waves == 1) {
-            second = tile >= last_m * nb1; wave = 0; r = second ? tile - last_m * nb1 : tile;
-        } else if (tile < A) {
-            second = false; wave = 0; r = tile;
-        } else {
-            const int p = tile - A;
-            const int k = p / (A + B);
-            if (k < n_waves - 2) {                                          // block k = [G1(k+1), G2(k)], both full
-                r = p - k * (A + B);
-                second = r >= A; wave = second ? k : k + 1; if (second) r -= A;
-            } else {                                                        // tail: G1(n-1) (maybe partial), G2(n-2), G2(n-1)
-                r = p - (n_waves - 2) * (A + B);
-                const int a_last = last_m * nb1;
-                if (r < a_last) { second = false; wave = n_waves - 1; }
-                else if (r < a_last + B) { second = true; wave = n_waves - 2; r -= a_last; }
-                else { second = true; wave = n_waves - 1; r -= a_last + B; }
+    const WaveOrder order_init(num_mblocks, max(1, fp.wave_mblocks), nb1, nb2);
+    const int tiles_all = healthy ? num_mblocks * (nb1 + 1 + nb2) : 0;
+    const int* arrive = reinterpret_cast<const int*>(rp.sym + rp.sl.pool_arrive);
+
+    // Requantisation tile, run by all eight epilogue warps: wait until every GEMM1 tile of the m-block is stored (each
+    // epilogue warp of each of its n_blocks tiles counts once), turn its bf16 rows into e4m3 with one scale per row, two
+    // rows per warp at a time, and release the m-block to GEMM2.
+    auto requantise_mblock = [&](int mb) -> bool {
+        const int valid = g1.mblock_valid[mb];
+        if (warp == 2 && lane == 0) {
+            int seen = 0;
+            const int target = nb1 * kEpilogueWarps;
+            const bool ok = wait_flag_ge(fp.l1_done + mb, target, false, status, g1.timeout_ns, &seen);
+            if (!ok) {
+                report_status(rp.scratch, rp.cl, MM_ERR_GRID_BARRIER_TIMEOUT, 4, mb, target, seen);
+                *abort_flag = 1;
+            }
+            s_misc[3] = ok ? 1 : 0;
+        }
+        named_bar_sync(2, kEpilogueThreads);
+        const bool ok = s_misc[3] != 0;
+        if (ok) {
+            __threadfence();
+            const int inter = g1.n_out, vecs = inter / 8;
+            const int ew = warp - 2;
+            for (int r = ew; r < valid; r += 2 * kEpilogueWarps) {
+                uint4 buf[2][8];
+                float inv[2], sc2[2];
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    const int64_t prow = static_cast<int64_t>(mb) * kBlockM + min(r + u * kEpilogueWarps, valid - 1);
+                    const float amax = __uint_as_float(__ldcg(g1.row_amax + prow));
+                    sc2[u] = fmaxf(__fdiv_rn(amax, 448.0f), 1.0e-4f);
+                    inv[u] = __fdiv_rn(1.0f, sc2[u]);
+                    const uint4* src = reinterpret_cast<const uint4*>(g1.act_bf16 + prow * inter);
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) { const int v = k * 32 + lane; if (v < vecs) buf[u][k] = __ldcg(src + v); }
+                }
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    if (r + u * kEpilogueWarps >= valid) continue;
+                    const int64_t prow = static_cast<int64_t>(mb) * kBlockM + r + u * kEpilogueWarps;
+                    const uint4* src = reinterpret_cast<const uint4*>(g1.act_bf16 + prow * inter);
+                    uint2* dst = reinterpret_cast<uint2*>(fp.act_fp8 + prow * inter);
+                    for (int v0 = 0; v0 < vecs; v0 += 32 * 8) {
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) {
+                            const int v = v0 + k * 32 + lane;
+                            if (v < vecs) {
+                                const uint4 d = (v0 == 0) ? buf[u][k] : __ldcg(src + v);
+                                uint2 o;
+                                o.x = pack4_e4m3(bf16_lo(d.x) * inv[u], bf16_hi(d.x) * inv[u], bf16_lo(d.y) * inv[u], bf16_hi(d.y) * inv[u]);
+                                o.y = pack4_e4m3(bf16_lo(d.z) * inv[u], bf16_hi(d.z) * inv[u], bf16_lo(d.w) * inv[u], bf16_hi(d.w) * inv[u]);
+                                dst[v] = o;
+                            }
+                        }
+                    }
+                    if (lane == 0) { fp.act_scale_w[prow] = sc2[u]; g1.row_amax[prow] = 0u; }
+                }
             }
         }
-        const int nbk = second ? nb2 : nb1;
-        mb = wave * wave_m + r / nbk;
-        nb = r - (r / nbk) * nbk;
+        named_bar_sync(2, kEpilogueThreads);             // all rows of the m-block are requantised
+        if (ok && warp == 2 && lane == 0) {
+            __threadfence();
+            atomicAdd(fp.l2_ready + mb, 4);              // GEMM2 producers wait for 4
+            atomicAdd(fp.grid_sync + 2, 1);
+        }
+        return ok;
     };
-    const int tiles_all = healthy ? num_mblocks * (g1.n_blocks + g2.n_blocks) : 0;
-    const int* arrive = reinterpret_cast<const int*>(rp.sym + rp.sl.pool_arrive);
 
     if (warp == 0) {
         // -------------------------------------------------------------- TMA producer
@@ -337,9 +411,12 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
         bool alive = true;
         // once every row has arrived (every m-block is requantised) no further per-tile polling is needed
         bool all_arrived = fp.gemm_only != 0, all_ready = false;
+        WaveOrder order = order_init;
         for (int tile = blockIdx.x; tile < tiles_all && alive; tile += gridDim.x) {
-            bool second; int mb, nb;
-            decode_tile(tile, second, mb, nb);
+            int kind, mb, nb;
+            order.seek(tile, kind, mb, nb);
+            if (kind == WaveOrder::kRequant) continue;          // epilogue warps only
+            const bool second = kind == WaveOrder::kG2;
             const GemmParams& g = second ? g2 : g1;
             const int e = g.mblock_expert[mb];
             const int k_blocks = g.kdim / kBlockK;
@@ -387,10 +464,12 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
         int stage = 0; uint32_t phase = 0;
         int acc = 0; uint32_t acc_phase = 0;
         bool alive = true;
+        WaveOrder order = order_init;
         for (int tile = blockIdx.x; tile < tiles_all && alive; tile += gridDim.x) {
-            bool second; int mb, nb;
-            decode_tile(tile, second, mb, nb);
-            const GemmParams& g = second ? g2 : g1;
+            int kind, mb, nb;
+            order.seek(tile, kind, mb, nb);
+            if (kind == WaveOrder::kRequant) continue;
+            const GemmParams& g = kind == WaveOrder::kG2 ? g2 : g1;
             const int k_blocks = g.kdim / kBlockK;
             if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, g.timeout_ns)) { alive = false; break; }
             tc_fence_after();
@@ -422,10 +501,16 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
         const bool do_clamp = g1.clamp < 3.0e38f;
         int acc = 0; uint32_t acc_phase = 0;
         bool alive = true;
+        WaveOrder order = order_init;
         for (int tile = blockIdx.x; tile < tiles_all && alive; tile += gridDim.x) {
             if (*abort_flag != 0) break;
-            bool second; int mb, nb;
-            decode_tile(tile, second, mb, nb);
+            int kind, mb, nb;
+            order.seek(tile, kind, mb, nb);
+            if (kind == WaveOrder::kRequant) {
+                if (!requantise_mblock(mb)) { alive = false; break; }
+                continue;
+            }
+            const bool second = kind == WaveOrder::kG2;
             const GemmParams& g = second ? g2 : g1;
             const int e = g.mblock_expert[mb];
             const int valid = g.mblock_valid[mb];
@@ -469,60 +554,11 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
             if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
 
             if (!second) {
-                // Count this CTA's finished GEMM1 tile of the m-block.  The CTA that finishes the last of the n_blocks tiles
-                // requantises the m-block's rows (their bf16 values and row amax are complete then) with all eight epilogue
-                // warps, two rows per warp at a time, and then releases the m-block to GEMM2.
-                named_bar_sync(2, kEpilogueThreads);                 // every warp's stores of this tile are issued
-                if (warp == 2 && lane == 0) {
+                // this warp's share of the tile (bf16 values, row amax) is stored: count it towards the m-block's GEMM1 total
+                __syncwarp();
+                if (lane == 0) {
                     __threadfence();
-                    s_misc[3] = (atomicAdd(fp.l1_done + mb, 1) + 1 == g1.n_blocks) ? 1 : 0;
-                }
-                named_bar_sync(2, kEpilogueThreads);
-                if (s_misc[3]) {
-                    __threadfence();
-                    const int inter = g1.n_out, vecs = inter / 8;
-                    const int ew = warp - 2;
-                    for (int r = ew; r < valid; r += 2 * kEpilogueWarps) {
-                        uint4 buf[2][8];
-                        float inv[2], sc2[2];
-#pragma unroll
-                        for (int u = 0; u < 2; ++u) {
-                            const int64_t prow = static_cast<int64_t>(mb) * kBlockM + min(r + u * kEpilogueWarps, valid - 1);
-                            const float amax = __uint_as_float(__ldcg(g1.row_amax + prow));
-                            sc2[u] = fmaxf(__fdiv_rn(amax, 448.0f), 1.0e-4f);
-                            inv[u] = __fdiv_rn(1.0f, sc2[u]);
-                            const uint4* src = reinterpret_cast<const uint4*>(g1.act_bf16 + prow * inter);
-#pragma unroll
-                            for (int k = 0; k < 8; ++k) { const int v = k * 32 + lane; if (v < vecs) buf[u][k] = __ldcg(src + v); }
-                        }
-#pragma unroll
-                        for (int u = 0; u < 2; ++u) {
-                            if (r + u * kEpilogueWarps >= valid) continue;
-                            const int64_t prow = static_cast<int64_t>(mb) * kBlockM + r + u * kEpilogueWarps;
-                            const uint4* src = reinterpret_cast<const uint4*>(g1.act_bf16 + prow * inter);
-                            uint2* dst = reinterpret_cast<uint2*>(fp.act_fp8 + prow * inter);
-                            for (int v0 = 0; v0 < vecs; v0 += 32 * 8) {
-#pragma unroll
-                                for (int k = 0; k < 8; ++k) {
-                                    const int v = v0 + k * 32 + lane;
-                                    if (v < vecs) {
-                                        const uint4 d = (v0 == 0) ? buf[u][k] : __ldcg(src + v);
-                                        uint2 o;
-                                        o.x = pack4_e4m3(bf16_lo(d.x) * inv[u], bf16_hi(d.x) * inv[u], bf16_lo(d.y) * inv[u], bf16_hi(d.y) * inv[u]);
-                                        o.y = pack4_e4m3(bf16_lo(d.z) * inv[u], bf16_hi(d.z) * inv[u], bf16_lo(d.w) * inv[u], bf16_hi(d.w) * inv[u]);
-                                        dst[v] = o;
-                                    }
-                                }
-                            }
-                            if (lane == 0) { fp.act_scale_w[prow] = sc2[u]; g1.row_amax[prow] = 0u; }
-                        }
-                    }
-                    named_bar_sync(2, kEpilogueThreads);             // all rows of the m-block are requantised
-                    if (warp == 2 && lane == 0) {
-                        __threadfence();
-                        atomicAdd(fp.l2_ready + mb, 4);              // GEMM2 producers wait for 4
-                        atomicAdd(fp.grid_sync + 2, 1);
-                    }
+                    red_release_gpu_add(fp.l1_done + mb, 1);
                 }
             }
         }

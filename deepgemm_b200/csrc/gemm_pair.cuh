@@ -11,9 +11,10 @@
 // An expert with an odd number of m-blocks leaves the second CTA of its last pair without rows: that CTA still feeds the
 // pipeline (it re-loads the first m-block's rows) and skips the stores.
 // Same arithmetic, epilogue and outputs (bit for bit) as gemm.cuh; same bounded waits and status words.
-// Measured on B200 at 1536 rows per expert (32 experts, hidden 4096, intermediate 2048): GEMM1 as fast as the one-CTA
-// kernel, GEMM2 6 % faster, the whole layer 1.4 % faster in a run long enough to sit at the power cap -- the tensor pipe
-// and the power cap bound these shapes, not the operand traffic this kernel saves.
+// Measured on B200 (hidden 4096, intermediate 2048): at 1536 rows per expert GEMM1 is as fast as with the one-CTA
+// kernel, GEMM2 6 % faster, the whole layer 1.4 % faster in a run long enough to sit at the power cap; at 768 rows per
+// expert (8 ranks, 4096 tokens each) GEMM1 is 9 % slower.  The tensor pipe and the power cap bound these shapes, not the
+// operand traffic this kernel saves, so the library uses it only on request (MEGAMOE_GEMM_PAIR=1).
 #pragma once
 #include "gemm.cuh"
 

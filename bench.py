@@ -265,6 +265,63 @@ def run_sweep(args):
         dist.destroy_process_group()
 
 
+def run_split_baseline(args):
+    """Expert-parallel size 1: the split pipeline of the reference's test (tests/test_mega_moe_dcu.py:188-300) against the
+    layer call on the same quantised inputs.  Without ranks there is no DeepEP dispatch / combine, so this compares only
+    what happens on one GPU: five launches with a bf16 [rows, 2I] round trip against the layer's launches."""
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    import megamoe
+    T = args.tokens
+    l1, l2, x_bf16, idx, w = make_rank_data(0, 1, T, dev)
+    sb = megamoe.get_symm_buffer_for_mega_moe(None, E, T, K, H, I)
+    xq, xs = megamoe.cast_to_fp8_channelwise(x_bf16)
+    sb.x[:T].copy_(xq); sb.x_sf[:T].copy_(xs); sb.topk_idx[:T].copy_(idx); sb.topk_weights[:T].copy_(w)
+    y = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
+    # the grouped GEMM wants W1 rows in natural order (gate rows, then up rows); the layer's tiling interleaves them
+    w1_nat = torch.empty((E, (2 * I) // 256, H // 128, 256, 128), dtype=torch.float8_e4m3fn, device=dev)
+    for e0 in range(0, E, 16):
+        w1_nat[e0:e0 + 16] = megamoe.pack_weights_tiled(megamoe.unpack_weights_tiled(l1[0][e0:e0 + 16], "l1", 2 * I), "l2")
+    counts = torch.bincount(idx.flatten(), minlength=E)
+    aligned = ((counts + 127) // 128 * 128).to(torch.int32)
+    rows = int(aligned.sum())
+    l1_out = torch.empty((rows, 2 * I), dtype=torch.bfloat16, device=dev)
+    a8 = torch.empty((rows, I), dtype=torch.float8_e4m3fn, device=dev)
+    a8s = torch.empty((rows,), device=dev)
+    l2_out = torch.empty((rows, H), dtype=torch.bfloat16, device=dev)
+    y2 = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
+
+    def split():
+        gx, gs, rw, mi, oi = megamoe.deepep_deepgemm_preprocess_channelwise(xq, xs, idx, w, aligned, rows)
+        megamoe.m_grouped_fp8_gemm_nt_contiguous((gx, gs), (w1_nat, l1[1]), l1_out, mi)
+        megamoe.swiglu_quant_channelwise_out(l1_out, rw, a8, a8s, None, num_per_channels=I, clamp_value=None)
+        megamoe.m_grouped_fp8_gemm_nt_contiguous((a8, a8s), l2, l2_out, mi)
+        megamoe.deepep_deepgemm_postprocess_channelwise(y2, l2_out, idx, w, oi, apply_topk_weights=False)
+
+    def timed(fn):
+        for _ in range(max(3, args.warmup)):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / args.steps
+
+    ms_layer = timed(lambda: megamoe.fp8_w8a8_mega_moe(y, l1, l2, sb))
+    ms_split = timed(split)
+    sb.check_status()
+    a, b = y.float().flatten(), y2.float().flatten()
+    cos = float(torch.nn.functional.cosine_similarity(a.double(), b.double(), dim=0))
+    print(json.dumps({"split_baseline": True, "workload": f"{E} experts top-{K} hidden {H} intermediate {I}, {T} tokens, EP=1",
+                      "layer_ms": round(ms_layer, 4), "split_pipeline_ms": round(ms_split, 4),
+                      "split_over_layer": round(ms_split / ms_layer, 3), "grouped_rows": rows, "cosine_layer_vs_split": round(cos, 6)}),
+          flush=True)
+    sb.destroy()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -276,6 +333,9 @@ def main():
     ap.add_argument("--experts", type=int, default=E, help="total experts (reduce only for small profiler captures)")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--split-baseline", action="store_true",
+                    help="one GPU: time the reference test's split pipeline (scatter, grouped GEMM, SwiGLU+quantise, grouped GEMM, "
+                         "gather) built from this library's kernels next to the layer call, on the same inputs")
     ap.add_argument("--sweep", default=None, help="comma-separated tokens-per-rank list: run the scaling sweep instead of the bench")
     args = ap.parse_args()
     globals()["E"] = args.experts
@@ -284,6 +344,9 @@ def main():
         return
     if args.sweep:
         run_sweep(args)
+        return
+    if args.split_baseline:
+        run_split_baseline(args)
         return
 
     dist, group, rank, world, local = init_dist(args.gpus)

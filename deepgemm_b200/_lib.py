@@ -21,7 +21,7 @@ MAX_RANKS = 16
 BLOCK_M = 128
 
 STATUS_NAMES = {0: "ok", 1: "rank barrier timeout", 2: "GEMM pipeline timeout", 3: "receive pool overflow",
-                4: "grid barrier timeout"}
+                4: "grid barrier timeout", 5: "m-grouped GEMM: a 128-row block mixes experts or has a hole"}
 
 # every symbol the header declares, with its signature
 _SIGNATURES = {
@@ -37,6 +37,8 @@ _SIGNATURES = {
     "mm_quant_per_token": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p]),
     "mm_deepep_scatter_channelwise": (c_int, [c_void_p] * 11 + [c_int] * 6 + [c_void_p]),
     "mm_deepep_gather_channelwise": (c_int, [c_void_p] * 5 + [c_int] * 5 + [c_void_p]),
+    "mm_m_grouped_fp8_gemm_nt_contiguous": (c_int, [c_void_p] * 6 + [c_int] * 4 + [c_void_p, c_void_p]),
+    "mm_swiglu_quant_channelwise": (c_int, [c_void_p] * 6 + [c_int, c_int, c_int, c_float, c_void_p]),
     "mm_fp8_mma_peak_probe": (c_int, [c_int, c_int, c_int, c_void_p, c_void_p, POINTER(ctypes.c_double)]),
     "mm_router_topk_quant": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "mm_fp8_w8a8_mega_moe": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,

@@ -20,6 +20,7 @@
 #include "misc.cuh"
 #include "probe.cuh"
 #include "route.cuh"
+#include "split_baseline.cuh"
 
 static_assert(MM_ABI_MAX_RANKS == MM_MAX_RANKS, "header and layout disagree");
 
@@ -363,6 +364,61 @@ int mm_deepep_gather_channelwise(void* recv_y, const void* l2_out, const void* r
     else
         mm::deepep_gather_kernel<int32_t><<<sms * 8, 256, 0, stream>>>(static_cast<__nv_bfloat16*>(recv_y), static_cast<const __nv_bfloat16*>(l2_out),
                                                                       recv_topk_ids, recv_topk_weights, output_index, recv_rows, topk, hidden, apply_topk_weights);
+    MM_LAUNCHED();
+    return 0;
+}
+
+int mm_m_grouped_fp8_gemm_nt_contiguous(const void* a_fp8, const float* a_scale, const void* w_tiled, const float* w_scale,
+                                        void* out_bf16, const int* m_indices, int rows, int N, int K, int E, int* work,
+                                        void* stream_) {
+    MM_REQUIRE(rows >= 0 && rows % MM_BLOCK_M == 0, "m-grouped GEMM: rows must be a multiple of %d (groups padded to it)", MM_BLOCK_M);
+    MM_REQUIRE(N > 0 && N % 64 == 0 && K > 0 && K % mm::kBlockK == 0 && E > 0, "m-grouped GEMM: need N %% 64 == 0, K %% 128 == 0, E > 0");
+    if (rows == 0) return 0;
+    MM_REQUIRE(a_fp8 && a_scale && w_tiled && w_scale && out_bf16 && m_indices && work, "m-grouped GEMM: null pointer");
+    MM_REQUIRE((reinterpret_cast<uintptr_t>(out_bf16) & 15) == 0, "m-grouped GEMM: output must be 16-byte aligned");
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    int sms = 0;
+    if (int rc = sm_count(&sms)) return rc;
+    if (int rc = ensure_gemm_attrs()) return rc;
+    const int blocks = rows / MM_BLOCK_M;
+    const int n_blocks = (N + mm::kBlockN - 1) / mm::kBlockN;
+    CUtensorMap tm_a, tm_b;
+    if (int rc = tensor_map_2d(a_fp8, (uint64_t)K, (uint64_t)rows, 128, &tm_a)) return rc;
+    if (int rc = tensor_map_2d(w_tiled, 128, (uint64_t)E * n_blocks * (K / 128) * 256, 256, &tm_b)) return rc;
+    MM_CUDA(cudaMemsetAsync(work, 0, 32 * sizeof(int), stream));
+    mm::mgroup_plan_kernel<<<(blocks * 32 + 255) / 256, 256, 0, stream>>>(m_indices, rows, E, work);
+    MM_LAUNCHED();
+    mm::GemmParams g;
+    memset(&g, 0, sizeof(g));
+    g.kdim = K; g.n_blocks = n_blocks; g.n_out = N; g.w_rows_per_expert = N;
+    g.plan = work + 16;
+    g.mblock_expert = work + 32;
+    g.mblock_valid = work + 32 + blocks;
+    g.w_scale = w_scale;
+    g.act_scale = a_scale;
+    g.out_rows = static_cast<__nv_bfloat16*>(out_bf16);
+    g.status = work;
+    g.timeout_ns = (uint64_t)g_pipe_ms.load() * 1000000ull;
+    g.E_loc = E;
+    mm::grouped_gemm_kernel<1><<<sms, mm::kGemmThreads, mm::kGemmSmemBytes, stream>>>(tm_a, tm_b, g);
+    MM_LAUNCHED();
+    return 0;
+}
+
+int mm_swiglu_quant_channelwise(const void* x_bf16, const float* weights, const int64_t* row_combine_ptrs, void* out_fp8,
+                                float* out_scale, void* out_bf16, int rows, int inter, int has_clamp, float clamp_value,
+                                void* stream_) {
+    MM_REQUIRE(rows >= 0 && inter > 0 && inter % 4 == 0, "swiglu_quant: need rows >= 0 and inter %% 4 == 0");
+    if (rows == 0) return 0;
+    MM_REQUIRE(x_bf16 && out_fp8 && out_scale, "swiglu_quant: null pointer");
+    MM_REQUIRE((reinterpret_cast<uintptr_t>(x_bf16) & 7) == 0 && (reinterpret_cast<uintptr_t>(out_fp8) & 3) == 0 &&
+               (reinterpret_cast<uintptr_t>(out_bf16) & 7) == 0, "swiglu_quant: x / out_bf16 must be 8-byte, out_fp8 4-byte aligned");
+    int sms = 0;
+    if (int rc = sm_count(&sms)) return rc;
+    int blocks = rows < sms * 8 ? rows : sms * 8;
+    mm::swiglu_quant_channelwise_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream_)>>>(
+        static_cast<const __nv_bfloat16*>(x_bf16), weights, row_combine_ptrs, static_cast<uint8_t*>(out_fp8), out_scale,
+        static_cast<__nv_bfloat16*>(out_bf16), rows, inter, has_clamp, clamp_value);
     MM_LAUNCHED();
     return 0;
 }

@@ -52,6 +52,7 @@ struct GemmParams {
     float clamp;               // +inf = none
     // kind 1
     const float* act_scale;    // [pool_rows]
+    __nv_bfloat16* out_rows;   // null: store into the source ranks' combine buffers; else out_rows[row][n_out] (plain grouped GEMM)
     uint64_t peers[MM_MAX_RANKS];
     int64_t combine_off;
     int T, H;
@@ -205,6 +206,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             bool alive = true;
             for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
                 const int mb = tile / p.n_blocks, nb = tile - mb * p.n_blocks;
+                if (p.mblock_valid[mb] == 0) continue;       // an m-block of padding rows only (plain grouped GEMM); all roles skip it
                 const int e = p.mblock_expert[mb];
                 const int a_row = mb * kBlockM;
                 // weights are stored tile by tile in the order this kernel consumes them:
@@ -231,6 +233,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             int acc = 0; uint32_t acc_phase = 0;
             bool alive = true;
             for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
+                if (p.mblock_valid[tile / p.n_blocks] == 0) continue;
                 if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.timeout_ns)) { alive = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * kBlockN;
@@ -269,6 +272,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             const int mb = tile / p.n_blocks, nb = tile - mb * p.n_blocks;
             const int e = p.mblock_expert[mb];
             const int valid = p.mblock_valid[mb];
+            if (valid == 0) continue;
             const int row = mb * kBlockM + et;
             const bool row_ok = et < valid;
             float* sc = scales_gen + acc * kBlockN;
@@ -287,11 +291,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             float row_scale = 0.0f, route_w = 0.0f;
             uint8_t* out_ptr = nullptr;                // kind 1: destination row in the source rank's combine buffer
             if (row_ok) {
-                const MmPoolMeta m = p.meta[row];
                 if (kKind == 0) {
+                    const MmPoolMeta m = p.meta[row];
                     row_scale = m.x_scale;
                     route_w = m.route_weight;
+                } else if (p.out_rows != nullptr) {     // plain grouped GEMM: row scale and a local output row
+                    row_scale = p.act_scale[row];
+                    out_ptr = reinterpret_cast<uint8_t*>(p.out_rows) + static_cast<int64_t>(row) * p.n_out * 2;
                 } else {
+                    const MmPoolMeta m = p.meta[row];
                     row_scale = p.act_scale[row];
                     const int src_rank = m.src_info >> 8, slot = m.src_info & 0xff;
                     out_ptr = reinterpret_cast<uint8_t*>(p.peers[src_rank]) + p.combine_off +

@@ -626,6 +626,91 @@ def deepep_deepgemm_postprocess_channelwise(recv_y: torch.Tensor, l2_out: torch.
             1 if apply_topk_weights else 0, _stream_ptr()))
 
 
+def m_grouped_fp8_gemm_nt_contiguous(a: Tuple[torch.Tensor, torch.Tensor], b: Tuple[torch.Tensor, torch.Tensor],
+                                     d: torch.Tensor, m_indices: torch.Tensor, check: bool = False) -> torch.Tensor:
+    """d[row] = bf16((a_fp8[row] . w[e]^T) * a_scale[row] * w_scale[e]) with e = m_indices[row]: the grouped GEMM of the
+    reference test's split baseline (its external `deepgemm.m_grouped_fp8_gemm_nt_contiguous`,
+    tests/test_mega_moe_dcu.py:245-250) with per-row and per-output-channel fp32 scales.  Rows are grouped by expert,
+    groups padded to 128 rows, padding rows have m_indices -1 and are left untouched.  The weight may be plain
+    [E, N, K] e4m3 (re-packed once and cached) or already tiled (pack_weights_tiled(w, "l2")).
+    check=True synchronises and raises if a 128-row block mixed experts."""
+    (a_q, a_s), (w, w_s) = a, b
+    for t in (a_q, a_s, w, w_s, d, m_indices):
+        _require_cuda(t, "m-grouped GEMM tensors")
+    if a_q.dtype != torch.float8_e4m3fn or w.dtype != torch.float8_e4m3fn or d.dtype != torch.bfloat16:
+        raise RuntimeError("m-grouped GEMM expects e4m3 operands and a bf16 output")
+    if a_s.dtype != torch.float32 or w_s.dtype != torch.float32 or m_indices.dtype != torch.int32:
+        raise RuntimeError("m-grouped GEMM expects fp32 scales and int32 m_indices")
+    rows, k = a_q.shape
+    e, n = w_s.shape
+    if d.shape != (rows, n) or a_s.numel() != rows or m_indices.numel() != rows:
+        raise RuntimeError("m-grouped GEMM shape mismatch")
+    if not (a_q.is_contiguous() and a_s.is_contiguous() and w_s.is_contiguous() and d.is_contiguous() and m_indices.is_contiguous()):
+        raise RuntimeError("m-grouped GEMM tensors must be contiguous")
+    if w.size(0) != e:
+        raise RuntimeError("m-grouped GEMM: weight and scale disagree on the number of experts")
+    w_tiled = _tiled_weight(w, n, k, "l2")
+    work = torch.empty((32 + 2 * (rows // _lib.BLOCK_M) + 2,), dtype=torch.int32, device=a_q.device)
+    with torch.cuda.device(a_q.device):
+        _lib.check(_lib.lib().mm_m_grouped_fp8_gemm_nt_contiguous(
+            a_q.data_ptr(), a_s.data_ptr(), w_tiled.data_ptr(), w_s.data_ptr(), d.data_ptr(), m_indices.data_ptr(),
+            rows, n, k, e, work.data_ptr(), _stream_ptr()))
+        if check:
+            out = (ctypes.c_int32 * 5)()
+            _lib.check(_lib.lib().mm_read_status(work.data_ptr(), _stream_ptr(), out))
+            if out[0] != 0:
+                raise _lib.MegaMoeError(f"device status {out[0]} ({_lib.STATUS_NAMES.get(out[0], '?')}): block={out[2]} "
+                                        f"expert={out[3]} valid rows={out[4]}")
+    return d
+
+
+def swiglu_quant_channelwise_out(x: torch.Tensor, topk_weights: Optional[torch.Tensor], out_fp8: torch.Tensor,
+                                 out_scale: torch.Tensor, out_bf16: Optional[torch.Tensor], *, num_per_channels: int,
+                                 use_col_major_scales: bool = False, round_scale: bool = False, ue8m0_scale: bool = False,
+                                 output_bf16: bool = False, clamp_value: Optional[float] = 10.0,
+                                 row_combine_ptrs: Optional[torch.Tensor] = None, verbose_build: bool = False):
+    """SwiGLU x route weight + per-row FP8 quantisation of a [rows, 2*hidden] bf16 (gate | up) tensor: the K2 step of the
+    reference's staged path and split baseline (megamoe/dcu_megamoe_large_opt/K2_fused/k2_fused.py:12-58)."""
+    if x.dim() != 2:
+        raise ValueError("x must be [rows, 2 * hidden]")
+    hidden = x.shape[1] // 2
+    if x.shape[1] != hidden * 2:
+        raise ValueError("x hidden dimension must be even")
+    if num_per_channels != hidden:
+        raise ValueError("K2 fused currently implements channelwise one-scale-per-row quant only")
+    if use_col_major_scales:
+        raise ValueError("K2 fused currently supports use_col_major_scales=False only")
+    if round_scale:
+        raise ValueError("K2 fused currently supports round_scale=False only")
+    if ue8m0_scale:
+        raise ValueError("K2 fused currently supports ue8m0_scale=False only")
+    _require_cuda(x, "x")
+    if x.dtype != torch.bfloat16 or out_fp8.dtype != torch.float8_e4m3fn or out_scale.dtype != torch.float32:
+        raise RuntimeError("swiglu_quant expects bf16 input, e4m3 output and fp32 scales")
+    rows = x.shape[0]
+    if tuple(out_fp8.shape) != (rows, hidden) or out_scale.numel() != rows or not out_fp8.is_contiguous() or not out_scale.is_contiguous():
+        raise RuntimeError("swiglu_quant output shape mismatch")
+    if output_bf16 and (out_bf16 is None or tuple(out_bf16.shape) != (rows, hidden) or out_bf16.dtype != torch.bfloat16
+                        or not out_bf16.is_contiguous()):
+        raise RuntimeError("output_bf16=True needs a contiguous bf16 [rows, hidden] out_bf16")
+    x = x.contiguous()
+    w = topk_weights.contiguous() if topk_weights is not None and topk_weights.numel() else None
+    if w is not None and (w.dtype != torch.float32 or w.numel() != rows):
+        raise RuntimeError("topk_weights must be fp32 [rows]")
+    ptrs = row_combine_ptrs.contiguous() if row_combine_ptrs is not None else None
+    if ptrs is not None and (ptrs.dtype != torch.int64 or ptrs.numel() != rows):
+        raise RuntimeError("row_combine_ptrs must be int64 [rows]")
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib().mm_swiglu_quant_channelwise(
+            x.data_ptr(), w.data_ptr() if w is not None else None, ptrs.data_ptr() if ptrs is not None else None,
+            out_fp8.data_ptr(), out_scale.data_ptr(), out_bf16.data_ptr() if output_bf16 else None, rows, hidden,
+            1 if clamp_value is not None else 0, float(clamp_value or 0.0), _stream_ptr()))
+    out_scale_view = out_scale.view(1, rows)
+    if output_bf16:
+        return out_fp8, out_scale_view, out_bf16
+    return out_fp8, out_scale_view
+
+
 __all__ = [
     "SymmBuffer",
     "cast_to_fp8_channelwise",
@@ -638,6 +723,8 @@ __all__ = [
     "unpack_weights_tiled",
     "deepep_deepgemm_preprocess_channelwise",
     "deepep_deepgemm_postprocess_channelwise",
+    "m_grouped_fp8_gemm_nt_contiguous",
+    "swiglu_quant_channelwise_out",
     "fp8_mega_moe",
     "fp8_w8a8_mega_moe",
     "fill_inputs_from_router",

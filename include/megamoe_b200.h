@@ -150,6 +150,26 @@ int mm_deepep_gather_channelwise(void* recv_y, const void* l2_out, const void* r
                                  const int* output_index, int recv_rows, int topk, int hidden, int topk_ids_i64,
                                  int apply_topk_weights, void* stream);
 
+/* The compute pieces of the reference test's split baseline (tests/test_mega_moe_dcu.py:188-300), so that it can be run
+ * on B200 beside the fused layer.
+ *
+ * mm_m_grouped_fp8_gemm_nt_contiguous: out[row, :] = bf16( (a_fp8[row, :] . w[e, :, :]^T) * a_scale[row] * w_scale[e, :] ),
+ *   e = m_indices[row]; stands in for the external deepgemm.m_grouped_fp8_gemm_nt_contiguous that the test calls
+ *   (tests/test_mega_moe_dcu.py:245-250, 274-279).  Rows are grouped by expert, every group padded to 128 rows, padding
+ *   rows carry m_indices = -1 (left untouched in `out`).  w_tiled: [E][ceil(N/256)][K/128][256][128] e4m3 (rows in natural
+ *   order, the "l2" packing of the Python helper pack_weights_tiled).  work: device int32[32 + 2 * rows / 128]; its first
+ *   five words are a status record readable with mm_read_status (code 5 = a block mixes experts or has a hole).
+ * mm_swiglu_quant_channelwise: the reference's K2 kernel (megamoe/dcu_megamoe_large_opt/K2_fused/k2_fused_ext.cu:254-377;
+ *   Python wrapper K2_fused/k2_fused.py:12-58): x bf16 [rows][2*inter] (gate | up) -> e4m3 [rows][inter] + f32 scale [rows],
+ *   y = gate * sigmoid(gate) * up * weights[row] (fp32; clamp: up two-sided, gate from above), scale = max(amax, 1e-4) / 448.
+ *   weights, row_combine_ptrs and out_bf16 may be null. */
+int mm_m_grouped_fp8_gemm_nt_contiguous(const void* a_fp8, const float* a_scale, const void* w_tiled, const float* w_scale,
+                                        void* out_bf16, const int* m_indices, int rows, int N, int K, int E, int* work,
+                                        void* stream);
+int mm_swiglu_quant_channelwise(const void* x_bf16, const float* weights, const int64_t* row_combine_ptrs, void* out_fp8,
+                                float* out_scale, void* out_bf16, int rows, int inter, int has_clamp, float clamp_value,
+                                void* stream);
+
 /* Measurement aid (no counterpart in the reference, whose test divides by a datasheet figure, tests/test_mega_moe_dcu.py:20-22):
  * launch a kernel that issues `iters` groups of eight dense FP8 MMAs (tcgen05 kind::f8f6f4, M128 x N256 x K32 per SM) from
  * operands resident in shared memory.  *flops_out receives the floating-point operations of the launch; time it with events

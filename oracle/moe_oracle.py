@@ -255,6 +255,31 @@ class LayerTrace:
     out_rows: List[torch.Tensor] = field(default_factory=list)  # bf16 per-route outputs in pool-row order
 
 
+def swiglu_quant_channelwise(gu: torch.Tensor, route_w: Optional[torch.Tensor], clamp: Optional[float]):
+    """K2 of the staged path and of the split baseline (megamoe/dcu_megamoe_large_opt/K2_fused/k2_fused_ext.cu:254-377):
+    gu [rows, 2I] holds bf16-representable gate | up values.  up is clamped two-sided, gate from above only;
+    y = gate * (1 / (1 + exp(-gate))) * up * weight in fp32; scale = max(amax, 1e-4) / 448; codes = e4m3(y * 448 / max(amax,
+    1e-4)) saturating.  A row with weight 0 gets zero codes and scale 1e-4 / 448 (lines 283-297).
+    Returns (codes e4m3 [rows, I], scale f32 [rows], y f32 [rows, I])."""
+    inter = gu.shape[1] // 2
+    g = gu[:, :inter].float(); u = gu[:, inter:].float()
+    if clamp is not None:
+        c = float(clamp)
+        u = u.clamp(-c, c); g = g.clamp(max=c)
+    w = torch.ones((gu.shape[0],)) if route_w is None else route_w.float()
+    act = g * (1.0 / (1.0 + torch.exp(-g))) * u * w.view(-1, 1)
+    amax = act.abs().amax(dim=1).clamp(min=1.0e-4)
+    s2 = amax / FP8_MAX
+    aq = (act * (FP8_MAX / amax).view(-1, 1)).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
+    if route_w is not None:
+        zero = w == 0
+        if bool(zero.any()):
+            aq = aq.clone(); s2 = s2.clone()
+            aq.view(torch.uint8)[zero] = 0
+            s2[zero] = 1.0e-4 / FP8_MAX
+    return aq, s2, act
+
+
 def moe_layer(x_q: Sequence[torch.Tensor], x_scale: Sequence[torch.Tensor],
               topk_idx: Sequence[torch.Tensor], topk_w: Sequence[torch.Tensor],
               w1_q: Sequence[torch.Tensor], w1_s: Sequence[torch.Tensor],
@@ -315,13 +340,7 @@ def moe_layer(x_q: Sequence[torch.Tensor], x_scale: Sequence[torch.Tensor],
                 s2 = (amax / FP8_MAX).clamp(min=1.0e-4)
                 aq = (act * (1.0 / s2).view(-1, 1)).to(torch.float8_e4m3fn)
             else:
-                g = _bf16_round(g); u = _bf16_round(u)
-                if activation_clamp is not None:
-                    u = u.clamp(-c, c); g = g.clamp(max=c)
-                act = g * (1.0 / (1.0 + torch.exp(-g))) * u * wr.view(-1, 1)
-                amax = act.abs().amax(dim=1).clamp(min=1.0e-4)
-                s2 = amax / FP8_MAX
-                aq = (act * (FP8_MAX / amax).view(-1, 1)).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
+                aq, s2, act = swiglu_quant_channelwise(torch.cat([_bf16_round(g), _bf16_round(u)], dim=1), wr, activation_clamp)
             # stage 6: GEMM2 on dequantised operands, bf16 per route
             a2 = aq.float() * s2.view(-1, 1)
             w2 = w2_q[o][le].float() * w2_s[o][le].view(-1, 1)

@@ -1,8 +1,8 @@
 """Generate the golden fixtures under tests/golden/.
 
-Run in a container that has the reference tree (default /root/reference, or $MEGAMOE_REFERENCE_ROOT):
+Run where a checkout of the reference project is available, giving its root directory:
 
-    python tests/golden/make_golden.py
+    python tests/golden/make_golden.py <reference root>          # or MEGAMOE_REFERENCE_ROOT=<reference root>
 
 Two kinds of fixture are written:
 
@@ -64,7 +64,9 @@ def edge_values():
 
 
 def main():
-    ref_root = os.environ.get("MEGAMOE_REFERENCE_ROOT", "/root/reference")
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("MEGAMOE_REFERENCE_ROOT")
+    if not ref_root or not os.path.isdir(ref_root):
+        raise SystemExit("usage: make_golden.py <root of the reference checkout>")
     ref = import_reference_megamoe(ref_root)
     out = {}
     g = torch.Generator().manual_seed(0)

@@ -100,3 +100,46 @@ def test_dsv4_flash_ep1_4096_tokens():
     assert torch.equal(y.view(torch.int16), y1[perm].view(torch.int16)), "permuting the tokens"
     assert not torch.isnan(y.float()).any()
     sb.destroy()
+
+
+def test_large_token_count_offsets_beyond_4_gib():
+    """131072 tokens x top-6 on 32 DSV4-shaped experts: 786k pool rows, so the byte offsets into the pool (3.2 GB), the
+    bf16 activations (3.2 GB) and the combine buffer (6.4 GB) pass 2^31 and 2^32.  Counts are checked bit-exactly against
+    torch; the outputs of sampled tokens (first, last, random) against the CPU oracle run on just those tokens -- a
+    token's output does not depend on the other tokens."""
+    if not torch.cuda.is_available():
+        pytest.fail("needs a CUDA device")
+    import megamoe
+    e, t = 32, 131072
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(9)
+    w1 = (torch.randn((e, 2 * I, H), generator=g, device=dev) / H ** 0.5).to(torch.bfloat16)
+    w2 = (torch.randn((e, H, I), generator=g, device=dev) / I ** 0.5).to(torch.bfloat16)
+    l1, l2 = megamoe.transform_fp8_weights_for_mega_moe(w1, w2)
+    del w1, w2
+    sb = megamoe.get_symm_buffer_for_mega_moe(None, e, t, K, H, I)
+    for t0 in range(0, t, 16384):                                     # fill in slices to bound the temporaries
+        x = torch.randn((16384, H), generator=g, device=dev).to(torch.bfloat16)
+        logits = torch.randn((16384, e), generator=g, device=dev)
+        xq, xs = megamoe.cast_to_fp8_channelwise(x)
+        wts, idx = torch.topk(torch.softmax(logits, dim=-1), K, dim=-1)
+        sb.x[t0:t0 + 16384].copy_(xq); sb.x_sf[t0:t0 + 16384].copy_(xs)
+        sb.topk_idx[t0:t0 + 16384].copy_(idx); sb.topk_weights[t0:t0 + 16384].copy_(wts / wts.sum(-1, keepdim=True))
+        del x, logits, xq, xs
+    stats = torch.zeros((e,), dtype=torch.int32, device=dev)
+    y = torch.full((t, H), float("nan"), dtype=torch.bfloat16, device=dev)
+    megamoe.fp8_w8a8_mega_moe(y, l1, l2, sb, cumulative_local_expert_recv_stats=stats)
+    sb.check_status()
+    assert torch.equal(stats, torch.bincount(sb.topk_idx[:t].flatten(), minlength=e).to(torch.int32))
+    assert int(stats.sum()) == t * K and not torch.isnan(y.float()).any()
+    dest = sb.scratch_view("dest_row", (sb.num_max_tokens_per_rank, K), torch.int32)[:t]
+    assert dest.flatten().long().unique().numel() == t * K and int(dest.max()) * H > 2 ** 31
+
+    pick = torch.cat([torch.arange(16), torch.arange(t - 16, t),
+                      torch.randint(0, t, (32,), generator=torch.Generator().manual_seed(3))]).to(dev)
+    w1p = megamoe.unpack_weights_tiled(l1[0], "l1", 2 * I).cpu()
+    w2p = megamoe.unpack_weights_tiled(l2[0], "l2", H).cpu()
+    ys, _, _ = orc.moe_layer([sb.x[pick].cpu()], [sb.x_sf[pick].cpu()], [sb.topk_idx[pick].cpu()], [sb.topk_weights[pick].cpu()],
+                             [w1p], [l1[1].cpu()], [w2p], [l2[1].cpu()], e, None, "fused")
+    mc.assert_end_to_end_close(y[pick].cpu(), ys[0], "sampled tokens of the 131072-token call")
+    sb.destroy()

@@ -428,11 +428,8 @@ int mm_fp8_mma_peak_probe(int iters, int operands, int cta_pair, int* status_dev
                "mm_fp8_mma_peak_probe: bad arguments");
     int sms = 0;
     if (int rc = sm_count(&sms)) return rc;
-    static bool attr_done = false;
-    if (!attr_done) {
-        MM_CUDA(cudaFuncSetAttribute(mm::fp8_mma_peak_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, mm::kABytes + mm::kBBytes));
-        attr_done = true;
-    }
+    // the attribute is per device; setting it on every call keeps multi-device processes correct (the call is cheap)
+    MM_CUDA(cudaFuncSetAttribute(mm::fp8_mma_peak_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, mm::kABytes + mm::kBBytes));
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     if (cta_pair) {
         sms = sms / 2 * 2;

@@ -421,7 +421,7 @@ def _tiled_weight(w: torch.Tensor, rows: int, k: int, which: str) -> torch.Tenso
     if not (native or marlin):
         raise RuntimeError(f"invalid {which.upper()} weight shape {tuple(w.shape)}, expected [expert, {rows}, {k}], "
                            f"Marlin [expert, {rows // 16}, {k * 16}] or tiled [expert, {nb}, {k // 128}, 256, 128]")
-    key = (w.data_ptr(), tuple(w.shape), w._version)
+    key = (w.data_ptr(), tuple(w.shape), w._version, which)      # the two packings of one tensor differ
     hit = _packed_weight_cache.get(key)
     if hit is None:
         if len(_packed_weight_cache) > 16:

@@ -581,10 +581,13 @@ int mm_fp8_w8a8_mega_moe(void* y, const void* w1, const float* s1, const void* w
         MM_STAGE(MM_STAGE_FUSED);
         return 0;
     }
-    // CTA-pair GEMMs (two m-blocks of one expert share each weight tile): opt-in with MEGAMOE_GEMM_PAIR=1.  Measured on
-    // B200 they tie with the one-CTA kernels at 1536 rows per expert and lose about 9 % on GEMM1 at 768 rows per expert
-    // (EP8, 4096 tokens per rank), where a third pair of an expert is often half empty.
-    bool pair_gemms = false;
+    // CTA-pair GEMMs (two m-blocks of one expert share each weight tile).  Measured on B200 (hidden 4096, intermediate
+    // 2048): with 192 rows per expert -- two m-blocks, the regime between HBM-bound and tensor-bound, where the one-CTA
+    // kernel streams every weight tile once from HBM and once more from L2 -- they take 10 % off both GEMMs; with 384 rows
+    // (three m-blocks: the second pair is half empty) they lose 7 % on GEMM1, with 768 rows 9 %, with 1536 rows they tie.
+    // So they are used when an expert is expected to hold two m-blocks; MEGAMOE_GEMM_PAIR=0/1 overrides.
+    const int64_t expected_routes = (int64_t)tokens_bound * K;        // per local expert: expected_routes / E_loc
+    bool pair_gemms = expected_routes > (int64_t)144 * E_loc && expected_routes <= (int64_t)256 * E_loc && sms >= 2;
     if (const char* v = getenv("MEGAMOE_GEMM_PAIR")) pair_gemms = v[0] == '1' && sms >= 2;
     CUtensorMap tm_w1h, tm_w2h;
     if (pair_gemms) {

@@ -11,10 +11,10 @@
 // An expert with an odd number of m-blocks leaves the second CTA of its last pair without rows: that CTA still feeds the
 // pipeline (it re-loads the first m-block's rows) and skips the stores.
 // Same arithmetic, epilogue and outputs (bit for bit) as gemm.cuh; same bounded waits and status words.
-// Measured on B200 (hidden 4096, intermediate 2048): at 1536 rows per expert GEMM1 is as fast as with the one-CTA
-// kernel, GEMM2 6 % faster, the whole layer 1.4 % faster in a run long enough to sit at the power cap; at 768 rows per
-// expert (8 ranks, 4096 tokens each) GEMM1 is 9 % slower.  The tensor pipe and the power cap bound these shapes, not the
-// operand traffic this kernel saves, so the library uses it only on request (MEGAMOE_GEMM_PAIR=1).
+// Measured on B200 (hidden 4096, intermediate 2048): with 192 rows per expert (two m-blocks: every weight tile is streamed
+// from HBM once instead of once from HBM and once from L2) both GEMMs are 10 % faster than with the one-CTA kernel; with
+// 384 rows (three m-blocks, a half-empty second pair) GEMM1 is 7 % slower, with 768 rows 9 % slower, with 1536 rows it
+// ties.  The host code therefore picks this kernel when an expert is expected to hold two m-blocks.
 #pragma once
 #include "gemm.cuh"
 

@@ -181,7 +181,10 @@ def run_reference_arm(args):
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": t_step * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"DSV4-Flash MoE layer E={E} top{K} H={H} I={I}, {tokens} tokens/rank, CPU sample", "l2": "n/a (CPU)"},
+        "config": {"workload": f"DSV4-Flash MoE layer: {E} experts top-{K} hidden {H} intermediate {I}, {tokens} tokens/rank, "
+                               f"EP={max(1, args.gpus)}, uniform N(0,1)-logit routing, W8A8 channelwise",
+                   "tokens_per_rank": tokens, "ep": max(1, args.gpus), "l2": "n/a (host cores)",
+                   "variant": "CPU restatement of the reference arithmetic on a bounded sample (rank 0's rows only)"},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,

@@ -467,6 +467,7 @@ def main():
     acc = {}
     n_rep = max(3, min(10, args.steps))
     for _ in range(n_rep):
+        barrier()                      # ranks start each timed call together, else the skew lands in the first cross-rank wait
         layer()
         for k_, v in _lib.stage_times().items():
             acc[k_] = acc.get(k_, 0.0) + v / n_rep

@@ -332,7 +332,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--tokens", type=int, default=4096, help="tokens per rank")
     ap.add_argument("--variant", default="auto", choices=["auto", "fused", "staged"],
-                    help="kernel variant: auto = the API's token threshold (fused up to 128 tokens, staged above)")
+                    help="kernel variant: auto = the API's token threshold (fused up to 256 tokens, staged above)")
     ap.add_argument("--experts", type=int, default=E, help="total experts (reduce only for small profiler captures)")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")

@@ -18,6 +18,7 @@ from __future__ import annotations
 import ctypes
 import math
 import os
+import weakref
 from types import SimpleNamespace
 from typing import Optional, Tuple
 
@@ -31,7 +32,9 @@ _LARGE_OPT_FORCE_VALUES = {"1", "true", "yes", "on", "large_opt", "3stage"}
 _LARGE_OPT_AUTO_VALUES = {"auto", "threshold", "adaptive"}
 _LARGE_OPT_ENV = "MEGAMOE_DCU_USE_LARGE_OPT_3STAGE"
 _LARGE_OPT_THRESHOLD_ENV = "MEGAMOE_DCU_LARGE_OPT_3STAGE_TOKEN_THRESHOLD"
-_LARGE_OPT_DEFAULT_THRESHOLD = 128
+# The reference switches at 128 tokens (megamoe/__init__.py:22).  Measured on B200 (2 ranks, DSV4-Flash shape) the fused
+# variant still wins at 192-256 tokens per rank (5-6 %), ties near 512 and loses beyond, or earlier with skewed routing.
+_LARGE_OPT_DEFAULT_THRESHOLD = 256
 # un-prefixed aliases of the reference's environment variables
 _ALIASES = {_LARGE_OPT_ENV: "MEGAMOE_USE_STAGED", _LARGE_OPT_THRESHOLD_ENV: "MEGAMOE_STAGED_TOKEN_THRESHOLD"}
 
@@ -421,14 +424,19 @@ def _tiled_weight(w: torch.Tensor, rows: int, k: int, which: str) -> torch.Tenso
     if not (native or marlin):
         raise RuntimeError(f"invalid {which.upper()} weight shape {tuple(w.shape)}, expected [expert, {rows}, {k}], "
                            f"Marlin [expert, {rows // 16}, {k * 16}] or tiled [expert, {nb}, {k // 128}, 256, 128]")
-    key = (w.data_ptr(), tuple(w.shape), w._version, which)      # the two packings of one tensor differ
+    # Keyed by address, shape, version counter and packing kind, and valid only while the SAME tensor object is alive: the
+    # allocator hands a freed address to the next tensor of that size, whose version counter also starts at 0.
+    key = (w.data_ptr(), tuple(w.shape), w._version, which)
     hit = _packed_weight_cache.get(key)
-    if hit is None:
-        if len(_packed_weight_cache) > 16:
-            _packed_weight_cache.clear()
-        hit = pack_weights_tiled(w.contiguous() if native else _marlin_inverse(w, rows, k), which)
-        _packed_weight_cache[key] = hit
-    return hit
+    if hit is not None and hit[0]() is w:
+        return hit[1]
+    for stale in [k_ for k_, v in _packed_weight_cache.items() if v[0]() is None]:
+        del _packed_weight_cache[stale]
+    if len(_packed_weight_cache) > 16:
+        _packed_weight_cache.clear()
+    packed = pack_weights_tiled(w.contiguous() if native else _marlin_inverse(w, rows, k), which)
+    _packed_weight_cache[key] = (weakref.ref(w), packed)
+    return packed
 
 
 def fp8_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer: SymmBuffer,

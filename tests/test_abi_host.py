@@ -115,6 +115,26 @@ def test_variant_choice_is_the_same_on_every_rank():
     assert sel(1, "auto", 100000, 2000, None, 4096, 6) is True
 
 
+def test_packed_weight_cache_is_bound_to_the_tensor_object():
+    """A freed weight's address, shape and version counter can all recur in the next weight tensor; the cache of re-packed
+    weights must then miss (it is valid only for the tensor object it was filled from)."""
+    import weakref
+    import torch
+    from deepgemm_b200 import megamoe as mm
+    g = torch.Generator().manual_seed(3)
+    w_old = torch.randint(0, 120, (2, 512, 128), generator=g, dtype=torch.uint8).view(torch.float8_e4m3fn)
+    w_new = torch.randint(0, 120, (2, 512, 128), generator=g, dtype=torch.uint8).view(torch.float8_e4m3fn)
+    packed_old = mm._tiled_weight(w_old, 512, 128, "l2")
+    assert mm._tiled_weight(w_old, 512, 128, "l2") is packed_old                      # same object: served from the cache
+    # plant w_old's packing under the key w_new would look up, as an address-reusing allocator would
+    mm._packed_weight_cache[(w_new.data_ptr(), tuple(w_new.shape), w_new._version, "l2")] = (weakref.ref(w_old), packed_old)
+    packed_new = mm._tiled_weight(w_new, 512, 128, "l2")
+    assert torch.equal(mm.unpack_weights_tiled(packed_new, "l2", 512).view(torch.uint8), w_new.view(torch.uint8))
+    assert not torch.equal(packed_new.view(torch.uint8), packed_old.view(torch.uint8))
+    # the two packings of one tensor are cached separately
+    assert not torch.equal(mm._tiled_weight(w_new, 512, 128, "l1").view(torch.uint8), packed_new.view(torch.uint8))
+
+
 def test_marlin_helper_matches_reference_fixture():
     import megamoe
     import numpy as np

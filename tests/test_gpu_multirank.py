@@ -92,12 +92,12 @@ def test_ep2_dsv4_shaped():
 
 
 def test_ep4_skewed():
-    _run(4, dict(E=32, K=6, H=1024, I=512, tokens=[200, 0, 77, 130], seed=24, zipf=True))
+    _run(4, dict(E=32, K=6, H=1024, I=512, tokens=[200, 0, 77, 130], seed=24, zipf=True, variant="staged"))
 
 
 def test_ep8_token_list_like_the_reference_cli():
     # the reference test's explicit per-rank list, e.g. 0,133,0,... (tests/test_mega_moe_dcu.py:405-419)
-    _run(8, dict(E=64, K=6, H=1024, I=512, tokens=[0, 133, 0, 64, 128, 1, 17, 96], seed=25))
+    _run(8, dict(E=64, K=6, H=1024, I=512, tokens=[0, 133, 0, 64, 128, 1, 17, 96], seed=25, variant="staged"))
 
 
 def _graph_worker(rank, world, port, cfg):

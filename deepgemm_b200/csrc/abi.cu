@@ -184,6 +184,8 @@ std::mutex g_stage_mu;
 cudaEvent_t g_stage_ev[MM_NUM_STAGES + 1];
 bool g_stage_ev_made = false;
 bool g_stage_recorded[MM_NUM_STAGES];
+int g_stage_order[MM_NUM_STAGES];      // stage ids in the order they were recorded by the last call
+int g_stage_count = 0;
 
 int stage_begin(cudaStream_t stream) {
     if (!g_stage_timing.load()) return 0;
@@ -193,14 +195,16 @@ int stage_begin(cudaStream_t stream) {
         g_stage_ev_made = true;
     }
     for (auto& r : g_stage_recorded) r = false;
+    g_stage_count = 0;
     MM_CUDA(cudaEventRecord(g_stage_ev[0], stream));
     return 0;
 }
-// called after the launch of stage `id`; stages are launched in increasing id order
+// called after the launch of stage `id` (each stage at most once per call, in any order)
 int stage_end(int id, cudaStream_t stream) {
     if (!g_stage_timing.load()) return 0;
     std::lock_guard<std::mutex> lk(g_stage_mu);
     MM_CUDA(cudaEventRecord(g_stage_ev[id + 1], stream));
+    if (!g_stage_recorded[id] && g_stage_count < MM_NUM_STAGES) g_stage_order[g_stage_count++] = id;
     g_stage_recorded[id] = true;
     return 0;
 }
@@ -556,9 +560,9 @@ int mm_fp8_w8a8_mega_moe(void* y, const void* w1, const float* s1, const void* w
         return 0;
     }
 
-    // Staged variant: GEMM1, requantisation, GEMM2, combine barrier and reduce are separate launches.  Measured on B200 this
-    // beats running them as one cooperative kernel (gemm_only mode of the fused kernel, MEGAMOE_STAGED_MERGED=1) at
-    // 4096-8192 tokens: there the in-epilogue requantisation and per-m-block dependency checks cost more than the launches.
+    // Staged variant: GEMM1, requantisation and GEMM2 are separate launches.  Measured on one B200 this beats running them as
+    // one cooperative kernel in wave order (gemm_only mode of the fused kernel, MEGAMOE_STAGED_MERGED=1) by 5-13 % at
+    // 4096-8192 tokens: the requantisation tiles and per-m-block dependency polls cost more than the launch gaps.
     static const bool split_gemms = [] { const char* v = getenv("MEGAMOE_STAGED_MERGED"); return !(v && v[0] == '1'); }();
     if (int rc = stage_begin(stream)) return rc;
 #define MM_STAGE(id) do { MM_LAUNCHED(); if (int rc_ = stage_end(id, stream)) return rc_; } while (0)
@@ -579,8 +583,11 @@ int mm_fp8_w8a8_mega_moe(void* y, const void* w1, const float* s1, const void* w
         MM_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(mm::mega_moe_fused_kernel), dim3(sms), dim3(mm::kFusedThreads),
                                             fused_args, mm::kGemmSmemBytes, stream));
         MM_STAGE(MM_STAGE_FUSED);
-        return 0;
-    }
+        // leave the per-m-block dependency counters zero for the next call (l1_done and l2_ready are adjacent regions)
+        const int64_t n_mb = rp.sl.pool_rows / MM_BLOCK_M;
+        MM_CUDA(cudaMemsetAsync(sc + rp.cl.l1_done, 0, (size_t)(rp.cl.l2_ready - rp.cl.l1_done + n_mb * 4), stream));
+        MM_CUDA(cudaMemsetAsync(sc + rp.cl.grid_sync + 2 * sizeof(int), 0, sizeof(int), stream));
+    } else {
     // CTA-pair GEMMs (two m-blocks of one expert share each weight tile).  Measured on B200 (hidden 4096, intermediate
     // 2048): with 192 rows per expert -- two m-blocks, the regime between HBM-bound and tensor-bound, where the one-CTA
     // kernel streams every weight tile once from HBM and once more from L2 -- they take 10 % off both GEMMs; with 384 rows
@@ -610,6 +617,7 @@ int mm_fp8_w8a8_mega_moe(void* y, const void* w1, const float* s1, const void* w
     if (pair_gemms) mm::grouped_gemm_pair_kernel<1><<<pair_grid, mm::kGemmThreads, mm::kPairSmemBytes, stream>>>(tm_act, tm_w2h, g2);
     else mm::grouped_gemm_kernel<1><<<sms, mm::kGemmThreads, mm::kGemmSmemBytes, stream>>>(tm_act, tm_w2, g2);
     MM_STAGE(MM_STAGE_GEMM2);
+    }   // split launches
     if (R > 1) {
         mm::rank_barrier_kernel<<<1, 32, 0, stream>>>(rp, MM_BAR_COMBINE);
         MM_STAGE(MM_STAGE_BARRIER_COMBINE);
@@ -661,15 +669,14 @@ int mm_get_stage_times(float* ms, int n) {
     MM_REQUIRE(ms && n >= MM_NUM_STAGES, "mm_get_stage_times: need room for %d floats", MM_NUM_STAGES);
     std::lock_guard<std::mutex> lk(g_stage_mu);
     MM_REQUIRE(g_stage_ev_made, "no timed call has been made");
-    int last = 0;
-    for (int i = 0; i < MM_NUM_STAGES; ++i) if (g_stage_recorded[i]) last = i + 1;
-    MM_CUDA(cudaEventSynchronize(g_stage_ev[last]));
-    int prev = 0;
-    for (int i = 0; i < MM_NUM_STAGES; ++i) {
-        ms[i] = -1.0f;
-        if (!g_stage_recorded[i]) continue;
-        MM_CUDA(cudaEventElapsedTime(&ms[i], g_stage_ev[prev], g_stage_ev[i + 1]));
-        prev = i + 1;
+    for (int i = 0; i < MM_NUM_STAGES; ++i) ms[i] = -1.0f;
+    if (g_stage_count == 0) return 0;
+    MM_CUDA(cudaEventSynchronize(g_stage_ev[g_stage_order[g_stage_count - 1] + 1]));
+    int prev = 0;                          // event index: 0 = start of the call, id + 1 = end of stage id
+    for (int k = 0; k < g_stage_count; ++k) {
+        const int id = g_stage_order[k];
+        MM_CUDA(cudaEventElapsedTime(&ms[id], g_stage_ev[prev], g_stage_ev[id + 1]));
+        prev = id + 1;
     }
     return 0;
 }

@@ -19,7 +19,8 @@
 //   5. grid barrier -> CTA 0 tells every rank "my combine stores are done"; wait for all ranks; top-k reduce; clean up.
 // Every wait is for tiles earlier in the tile order (or for dispatch), and every role of a CTA walks its tiles in order,
 // so the waits cannot form a cycle.  Every wait is bounded and ends in a status code, never in a hang.
-// gemm_only = 1 starts at step 4 after the staged routing / dispatch launches (any token count).
+// gemm_only = 1 runs step 4 alone, between the staged routing / dispatch launches and the staged combine barrier and
+// reduce launches (any token count); the host resets the dependency counters afterwards.
 #pragma once
 #include "gemm.cuh"
 #include "misc.cuh"
@@ -564,10 +565,12 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
         }
     }
 
-    // ------------------------------------------------------------------ phase 5: all ranks' combine stores done
     __threadfence_system();
     __syncthreads();
     if (tid == 0) stamp(9);
+    // gemm_only: the combine barrier, the reduce and the counter reset are separate launches after this kernel
+    if (!fp.gemm_only) {
+    // ------------------------------------------------------------------ phase 5: all ranks' combine stores done
     const int grid_target = static_cast<int>(gridDim.x) * (fused_calls + 1);
     if (tid == 0) red_release_gpu_add(fp.grid_sync, 1);
     if (blockIdx.x == 0) {
@@ -639,10 +642,11 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
         if (blockIdx.x == 0 && tid == 0) {
             arr[arrive_total_slot] = 0;
             fp.grid_sync[2] = 0;
-            if (!fp.gemm_only) reinterpret_cast<int*>(rp.scratch + rp.cl.epoch)[0] = epoch;
+            reinterpret_cast<int*>(rp.scratch + rp.cl.epoch)[0] = epoch;
             fp.grid_sync[1] = fused_calls + 1;
         }
     }
+    }   // !gemm_only
     if (*abort_flag != 0) {
         const uint64_t t0 = global_timer_ns();
         while (global_timer_ns() - t0 < 1000000ull) __nanosleep(1000);

@@ -20,19 +20,15 @@ import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
-for p in (ROOT, os.path.join(ROOT, "tests")):
-    if p not in sys.path:
-        sys.path.insert(0, p)
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
 
 import torch  # noqa: E402
 
 E, K, H, I = 256, 6, 4096, 2048
 METRIC, UNIT = "moe_layer_tokens_per_s", "tokens/s"
 FLOP_PER_ROW = 2 * 3 * H * I                     # 50.33 MFLOP per routed row (GEMM1 33.55 + GEMM2 16.78)
-# DRAM read+write bytes of one GEMM1 launch per expert processed, from the ncu capture summarised in
-# profiles/grouped_gemm_dsv4_32experts_512tok.md (566.9 MB for 32 experts with 96 rows each; traffic grows with the
-# experts processed, so a launch over n experts moves n times this)
-GEMM1_DRAM_TRAFFIC_BYTES_PER_EXPERT = 566.9e6 / 32
+PARITY_SAMPLES = 4                               # tokens per rank checked against the CPU oracle after the timed region
 
 
 def measured_peaks():
@@ -42,6 +38,88 @@ def measured_peaks():
             d = json.load(f)
         return float(d["hbm_gbs"]), "measured"
     return 6650.0, "fallback"
+
+
+def measured_bf16_tflops():
+    """Dense bf16 burst figure of the machine-readable peak file (None if absent); twice it is the usual FP8 estimate."""
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f).get("bf16_tflops", 0.0)) or None
+    return None
+
+
+def parity_block(dist, group, rank, world, dev, sb, l1, l2, y, stats, tokens, n_samples=PARITY_SAMPLES):
+    """Correctness of the run that was just timed, computed outside the timed region at every N:
+      counts_equal      per-expert receive statistics == bincount of all ranks' top-k indices (bit-exact routing counts);
+      max_abs_over_rms, cosine   of `n_samples` tokens per rank against the CPU oracle (oracle/moe_oracle.py) run on just those
+                        tokens -- a token's output depends on no other token.  Every rank runs the oracle for the sampled
+                        routes that hit ITS experts (its weights never leave the rank); the per-route rows are summed over
+                        ranks, then reduced in slot order as the layer does.
+    The literal acceptance bar is max_abs <= 2e-2 * rms and cosine >= 0.999; `ok` is the run's pass/fail: counts equal,
+    cosine >= 0.999 and no element off by more than 0.1 * rms (an FP8 activation code that flips on a rounding tie moves one
+    output row by a few percent of rms, so the literal figure is reported beside it rather than asserted)."""
+    import megamoe
+    from oracle import moe_oracle as orc
+    e_loc = E // world
+    T = tokens
+
+    def gather(t):
+        if dist is None:
+            return t
+        out = [torch.empty_like(t) for _ in range(world)]
+        dist.all_gather(out, t.contiguous())
+        return torch.cat(out, dim=0)
+
+    idx_all = gather(sb.topk_idx[:T])
+    w_all = gather(sb.topk_weights[:T])
+    valid = (idx_all >= 0) & (idx_all < E) & (w_all != 0)
+    counts = torch.bincount(idx_all[valid].flatten(), minlength=E)[rank * e_loc:(rank + 1) * e_loc].to(torch.int32)
+    counts_equal = bool(torch.equal(counts, stats))
+
+    gp = torch.Generator().manual_seed(4242 + rank)
+    pick = torch.unique(torch.cat([torch.tensor([0, T - 1]), torch.randint(0, T, (max(n_samples - 2, 0),), generator=gp)]))[:n_samples]
+    while pick.numel() < n_samples:                                     # duplicates removed above: top up deterministically
+        pick = torch.unique(torch.cat([pick, torch.tensor([(int(pick[-1]) + 17) % T])]))
+    pick = pick.to(dev)
+    xq = gather(sb.x[pick].view(torch.uint8)).cpu().view(torch.float8_e4m3fn)
+    xs = gather(sb.x_sf[pick]).cpu()
+    idx_s = gather(sb.topk_idx[pick]).cpu()
+    w_s = gather(sb.topk_weights[pick]).cpu()
+    n_tok = idx_s.shape[0]
+    mine = (idx_s >= rank * e_loc) & (idx_s < (rank + 1) * e_loc) & (w_s != 0)
+    touched = torch.unique(idx_s[mine]) - rank * e_loc                  # local indices of the experts the samples hit here
+    contrib = torch.zeros((n_tok, K, H), dtype=torch.float32)
+    if touched.numel():
+        remap = torch.full((E,), -1, dtype=torch.int64)
+        remap[touched + rank * e_loc] = torch.arange(touched.numel())
+        idx_local = torch.where(mine, remap[idx_s.clamp(0, E - 1)], torch.full_like(idx_s, -1))
+        sel = touched.to(dev)
+        w1p = megamoe.unpack_weights_tiled(l1[0][sel], "l1", 2 * I).cpu()
+        w2p = megamoe.unpack_weights_tiled(l2[0][sel], "l2", H).cpu()
+        _, lay, tr = orc.moe_layer([xq], [xs], [idx_local], [w_s], [w1p], [l1[1][sel].cpu()], [w2p], [l2[1][sel].cpu()],
+                                   int(touched.numel()), None, "fused", trace=True)
+        rows = torch.from_numpy((lay.row_src_rank[0] >= 0).nonzero()[0])
+        tt = torch.from_numpy(lay.row_src_token[0][rows.numpy()].astype("int64"))
+        kk = torch.from_numpy(lay.row_src_slot[0][rows.numpy()].astype("int64"))
+        contrib[tt, kk] = tr.out_rows[0][rows].float()
+    contrib = contrib.to(dev)
+    if dist is not None:
+        dist.all_reduce(contrib)
+    mine_rows = contrib[rank * n_samples:(rank + 1) * n_samples]
+    acc = torch.zeros((n_samples, H), dtype=torch.float32, device=dev)
+    for s_ in range(K):                                                 # slot order, fp32, one bf16 rounding
+        acc += mine_rows[:, s_]
+    y_ref = acc.to(torch.bfloat16)
+    err, cos = orc.parity_metrics(y[pick].cpu(), y_ref.cpu())
+    vals = torch.tensor([err, -cos, 0.0 if counts_equal else 1.0], dtype=torch.float64, device=dev)
+    if dist is not None:
+        dist.all_reduce(vals, op=dist.ReduceOp.MAX)
+    err, cos, bad_counts = float(vals[0]), -float(vals[1]), float(vals[2]) > 0
+    return {"counts_equal": not bad_counts, "max_abs_over_rms": round(err, 5), "cosine": round(cos, 7),
+            "sampled_tokens_per_rank": n_samples, "oracle": "oracle/moe_oracle.py, numerics 'fused', on the sampled tokens",
+            "literal_bar": {"max_abs_over_rms": 2e-2, "cosine": 0.999, "met": bool(err <= 2e-2 and cos >= 0.999)},
+            "ok": bool((not bad_counts) and cos >= 0.999 and err <= 0.1)}
 
 
 class ClockSampler:
@@ -191,10 +269,39 @@ def run_reference_arm(args):
     }))
 
 
+def nvlink_store_probe(dist, group, rank, world, dev, sb):
+    """GB/s per direction of this library's own plain 16-byte stores into peers' receive pools (between layer calls): to
+    the next rank only and spread over all peers, every rank storing at once; the slowest rank's best of three."""
+    import ctypes
+    from deepgemm_b200 import _lib
+    lib = _lib.lib()
+    stream = torch.cuda.current_stream().cuda_stream
+    pool_bytes = sb.pool_rows * H // 512 * 512
+    peers = [p_ for r_, p_ in enumerate(sb.handle.buffer_ptrs) if r_ != rank]
+    probe = {}
+    for name, dsts, nbytes in (("one_peer", [sb.handle.buffer_ptrs[(rank + 1) % world]], min(pool_bytes, 256 << 20)),
+                               ("all_peers", peers, min(pool_bytes, (256 << 20) // len(peers) // 512 * 512))):
+        arr = (ctypes.c_uint64 * len(dsts))(*[d + sb._sym_off["pool_x"] for d in dsts])
+        best = 0.0
+        for _ in range(3):
+            torch.cuda.synchronize(); dist.barrier(group); torch.cuda.synchronize()
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            _lib.check(lib.mm_peer_store_probe(arr, len(dsts), nbytes, stream))
+            t1.record()
+            torch.cuda.synchronize()
+            best = max(best, nbytes * len(dsts) / (t0.elapsed_time(t1) * 1e-3) / 1e9)
+        t = torch.tensor([best], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        probe[name] = round(float(t.item()), 1)
+    torch.cuda.synchronize(); dist.barrier(group)
+    return probe
+
+
 def run_sweep(args):
     """--sweep: the scaling sweep of the layer (tokens per rank x routing skew) at the launched EP size.  One JSON line per
     point from rank 0: tokens/s, FP8 TFLOP/s, NVLink GB/s per rank and the three roofline times (tensor at the measured FP8
-    peak, HBM at the measured copy peak, NVLink at the measured 770 GB/s per direction); max over ranks, CUDA events."""
+    peak, HBM at the measured copy peak, NVLink at the rate of this library's own store probe); max over ranks, CUDA events."""
     dist, group, rank, world, local = init_dist(args.gpus)
     dev = torch.device("cuda", local)
     import megamoe
@@ -207,6 +314,9 @@ def run_sweep(args):
     fp8_peak = _lib.fp8_mma_peak_tflops()                                   # all-ones operands: the burst rate
     fp8_peak_data = _lib.fp8_mma_peak_tflops(random_operands=True)          # random operands: what real data can reach
     hbm_peak, _ = measured_peaks()
+    # NVLink denominator: this library's own store probe spread over all peers (measured here, printed in every line)
+    nvl_probe = nvlink_store_probe(dist, group, rank, world, dev, sb) if world > 1 else {"one_peer": None, "all_peers": None}
+    nvl_gbs = nvl_probe["all_peers"] or 1.0
     g = torch.Generator(device=dev).manual_seed(2000 + rank)
     gp = torch.Generator().manual_seed(12345)
     pop = torch.empty(E)
@@ -249,7 +359,7 @@ def run_sweep(args):
             hbm_bytes = float(allv[:, 2].max()) * (3 * H * I + 4 * (2 * I + H)) + rows_max * (H + 4 + (I + 4) * 2 + 2 * H)
             t_hbm = hbm_bytes / (hbm_peak * 1e9) * 1e3
             remote = rows_max * (world - 1) / world
-            t_nvl = remote * (H + 16 + 2 * H) / 770e9 * 1e3          # dispatch in + combine out share a direction in time
+            t_nvl = remote * (H + 16 + 2 * H) / (nvl_gbs * 1e9) * 1e3   # dispatch in + combine out share a direction in time
             t_roof = max(t_tensor, t_hbm, t_nvl)
             if rank == 0:
                 print(json.dumps({
@@ -258,10 +368,11 @@ def run_sweep(args):
                     "fp8_frac_of_measured_peak_per_gpu": round(rows_max * FLOP_PER_ROW / (ms * 1e-3) / 1e12 / fp8_peak_data, 3),
                     "fp8_peak_tflops": {"ones_operands": round(fp8_peak, 1), "random_operands": round(fp8_peak_data, 1)},
                     "nvlink_gbs_per_rank": round(remote * (H + 16 + 2 * H) / (ms * 1e-3) / 1e9, 1),
+                    "nvlink_store_probe_gbs": nvl_probe,
                     "max_rows_per_expert": int(allv[:, 3].max()), "rows_max_rank": int(rows_max),
                     "roof_ms": {"tensor": round(t_tensor, 4), "hbm": round(t_hbm, 4), "nvlink": round(t_nvl, 4)},
                     "frac_of_roofline": round(t_roof / ms, 3),
-                    "variant": "fused" if (T <= sb._large_opt_3stage_threshold and T * K <= 4096) else "staged"}), flush=True)
+                    "variant": "fused" if T <= sb._large_opt_3stage_threshold else "staged"}), flush=True)
     sb.destroy()
     if dist is not None:
         dist.barrier(group)
@@ -331,14 +442,17 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--tokens", type=int, default=4096, help="tokens per rank")
-    ap.add_argument("--variant", default="auto", choices=["auto", "fused", "staged"],
-                    help="kernel variant: auto = the API's token threshold (fused up to 256 tokens, staged above)")
+    ap.add_argument("--variant", default="auto", choices=["auto", "fused", "staged", "split"],
+                    help="kernel variant: auto = the API's token threshold (fused up to 256 tokens, staged above); "
+                         "split = the staged variant as separate dispatch / GEMM1 / requantisation / GEMM2 launches")
     ap.add_argument("--experts", type=int, default=E, help="total experts (reduce only for small profiler captures)")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--split-baseline", action="store_true",
                     help="one GPU: time the reference test's split pipeline (scatter, grouped GEMM, SwiGLU+quantise, grouped GEMM, "
                          "gather) built from this library's kernels next to the layer call, on the same inputs")
+    ap.add_argument("--profile-only", action="store_true",
+                    help="device-resident arm only (no end-to-end arm, no parity or CPU baseline): the command line for ncu captures")
     ap.add_argument("--sweep", default=None, help="comma-separated tokens-per-rank list: run the scaling sweep instead of the bench")
     args = ap.parse_args()
     globals()["E"] = args.experts
@@ -354,6 +468,7 @@ def main():
 
     dist, group, rank, world, local = init_dist(args.gpus)
     dev = torch.device("cuda", local)
+    import ctypes
     import megamoe
     from deepgemm_b200 import _lib
     T = args.tokens
@@ -361,8 +476,10 @@ def main():
     l1, l2, x_bf16, idx, w = make_rank_data(rank, world, T, dev)
     sb = megamoe.get_symm_buffer_for_mega_moe(group, E, T, K, H, I)
     if args.variant != "auto":
-        sb._large_opt_3stage_mode = {"fused": "off", "staged": "force"}[args.variant]
-    staged = megamoe._large_opt_3stage_selected(T, sb._large_opt_3stage_mode, sb._large_opt_3stage_threshold) or T * K > 4096
+        sb._large_opt_3stage_mode = {"fused": "off", "staged": "force", "split": "force"}[args.variant]
+        sb._staged_split = args.variant == "split"
+    staged = megamoe._large_opt_3stage_selected(T, sb._large_opt_3stage_mode, sb._large_opt_3stage_threshold)
+    variant = ("staged-split" if sb._staged_split else "staged") if staged else "fused"
     y = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
     stream = torch.cuda.current_stream().cuda_stream
     lib = _lib.lib()
@@ -406,11 +523,22 @@ def main():
     launches = _lib.launch_count() - launches0
     ms_step = max_over_ranks(ev0.elapsed_time(ev1) / args.steps)
     sb.check_status()
+    if args.profile_only:
+        sampler.stop()
+        if rank == 0:
+            print(json.dumps({"profile_only": True, "ms_per_step": ms_step, "gpu_launches": launches, "experts": E, "tokens_per_rank": T,
+                              "ep": world, "variant": variant}), flush=True)
+        sb.destroy()
+        if dist is not None:
+            dist.barrier(group)
+            dist.destroy_process_group()
+        return
 
     # ---- end-to-end arm: host buffers in, host buffer out, every step ------------------------------------------
     # Every step copies its inputs from pinned host memory (bf16 activations, top-k indices and weights), quantises,
     # runs the layer and copies y back to pinned host memory.  The three phases run on three streams with double
     # buffering, so step i+1's upload and step i-1's download overlap step i's compute, as a serving loop would do.
+    # compute=False runs the same copies on the same streams without the kernels: the copy floor of this box.
     hx = x_bf16.cpu().pin_memory(); hidx = idx.cpu().pin_memory(); hw = w.cpu().pin_memory()
     hy = [torch.empty((T, H), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
     dx = [torch.empty_like(x_bf16) for _ in range(2)]
@@ -426,7 +554,7 @@ def main():
     for e in ev_free + ev_out:
         e.record(s_main)
 
-    def e2e_step(i):
+    def e2e_step(i, compute=True):
         b = i & 1
         with torch.cuda.stream(s_in):
             s_in.wait_event(ev_free[b])
@@ -435,34 +563,41 @@ def main():
             dw[b].copy_(hw, non_blocking=True)
             ev_ready[b].record(s_in)
         s_main.wait_event(ev_ready[b])
-        sb.topk_idx[:T].copy_(didx[b], non_blocking=True)
-        sb.topk_weights[:T].copy_(dw[b], non_blocking=True)
-        quantise_into_buffer(dx[b])
+        if compute:
+            sb.topk_idx[:T].copy_(didx[b], non_blocking=True)
+            sb.topk_weights[:T].copy_(dw[b], non_blocking=True)
+            quantise_into_buffer(dx[b])
         ev_free[b].record(s_main)
         s_main.wait_event(ev_out[b])                      # the previous y in this buffer has left the device
-        megamoe.fp8_w8a8_mega_moe(dy[b], l1, l2, sb)
+        if compute:
+            megamoe.fp8_w8a8_mega_moe(dy[b], l1, l2, sb)
         ev_done[b].record(s_main)
         with torch.cuda.stream(s_out):
             s_out.wait_event(ev_done[b])
             hy[b].copy_(dy[b], non_blocking=True)
             ev_out[b].record(s_out)
 
-    for i in range(4):
-        e2e_step(i)
-    barrier()
-    ev2, ev3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ev2.record(s_main)
-    for i in range(args.steps):
-        e2e_step(i)
-    s_main.wait_event(ev_out[0]); s_main.wait_event(ev_out[1])   # the timed region ends when the last y is on the host
-    ev3.record(s_main)
-    barrier()
-    e2e_ms = max_over_ranks(ev2.elapsed_time(ev3) / args.steps)
+    def time_e2e(compute):
+        for i in range(4):
+            e2e_step(i, compute)
+        barrier()
+        ev2, ev3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev2.record(s_main)
+        for i in range(args.steps):
+            e2e_step(i, compute)
+        s_main.wait_event(ev_out[0]); s_main.wait_event(ev_out[1])   # the timed region ends when the last y is on the host
+        ev3.record(s_main)
+        barrier()
+        return max_over_ranks(ev2.elapsed_time(ev3) / args.steps)
+
+    e2e_ms = time_e2e(True)
     clocks = sampler.stop()
+    copy_floor_ms = time_e2e(False)
     h2d = T * H * 2 + T * K * 8 + T * K * 4
     d2h = T * H * 2
 
     # ---- per-stage times (CUDA events recorded by the library on the launching stream) --------------------------
+    sb.topk_idx[:T].copy_(idx); sb.topk_weights[:T].copy_(w); quantise_into_buffer(x_bf16)
     lib.mm_set_stage_timing(1)
     acc = {}
     n_rep = max(3, min(10, args.steps))
@@ -474,39 +609,52 @@ def main():
     lib.mm_set_stage_timing(0)
     stats = torch.zeros((e_loc,), dtype=torch.int32, device=dev)
     megamoe.fp8_w8a8_mega_moe(y, l1, l2, sb, cumulative_local_expert_recv_stats=stats)
+    torch.cuda.synchronize()
+    sb.check_status()
     rows_recv = int(stats.sum().item())
     touched = int((stats > 0).sum().item())
-    split = "gemm1" in acc        # staged: GEMM1 / requant / GEMM2 / reduce are separate launches (unless MEGAMOE_STAGED_MERGED=1)
-    gemm1_ms = max_over_ranks(acc["gemm1"] if split else acc["fused"])
-    # algorithmic bytes of one GEMM1 launch: FP8 gate+up weights and their scales of the touched experts, the received
-    # FP8 rows with their 16-byte metadata, the bf16 activations written
-    gemm1_bytes = touched * (2 * I * H + 4 * 2 * I) + rows_recv * (H + 16) + rows_recv * I * 2
-    kernel_name = "grouped_gemm_kernel<0> (GEMM1 + SwiGLU)"
-    traffic = GEMM1_DRAM_TRAFFIC_BYTES_PER_EXPERT * touched
-    if not split:
-        # the persistent kernel moves the whole layer's bytes (formula of the reference's own test,
+    parity = parity_block(dist, group, rank, world, dev, sb, l1, l2, y, stats, T, min(PARITY_SAMPLES, T))
+
+    # ---- roofline of the dominant kernel ----------------------------------------------------------------------------
+    split = "gemm1" in acc        # separate GEMM1 / requantisation / GEMM2 launches (MEGAMOE_STAGED_SPLIT=1)
+    kernel_ms = max_over_ranks(acc["gemm1"] if split else acc["fused"])
+    if split:
+        # GEMM1 launch: FP8 gate+up weights and scales of the touched experts, the received FP8 rows with their 16-byte
+        # metadata, the bf16 activations written
+        kernel_bytes = touched * (2 * I * H + 4 * 2 * I) + rows_recv * (H + 16) + rows_recv * I * 2
+        kernel_flops = rows_recv * 2 * H * 2 * I
+        kernel_name = "grouped_gemm_kernel<0> (GEMM1 + SwiGLU)"
+    else:
+        # the layer kernel moves the whole layer's bytes (formula of the reference's own test,
         # tests/test_mega_moe_dcu.py:352-364): weights + scales, FP8 rows in, FP8 activations written and read, bf16 rows out
-        kernel_name = ("mega_moe_fused_kernel (GEMM1 + requantisation + GEMM2 + combine reduce)" if staged
+        kernel_bytes = touched * (3 * H * I + 4 * (2 * I + H)) + rows_recv * (H + 4) + rows_recv * (I + 4) * 2 + rows_recv * H * 2
+        kernel_flops = rows_recv * FLOP_PER_ROW
+        kernel_name = ("mega_moe_fused_kernel (NVLink push + GEMM1 + requantisation + GEMM2 + combine stores)" if staged
                        else "mega_moe_fused_kernel (whole layer)")
-        gemm1_bytes = touched * (3 * H * I + 4 * (2 * I + H)) + rows_recv * (H + 4) + rows_recv * (I + 4) * 2 + rows_recv * H * 2
-        traffic = None
     hbm_peak, peak_kind = measured_peaks()
-    achieved = gemm1_bytes / (gemm1_ms * 1e-3) / 1e9
+    achieved = kernel_bytes / (kernel_ms * 1e-3) / 1e9
     roofline = {"kernel": kernel_name, "bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
-                "frac": achieved / hbm_peak, "peak_kind": f"of {peak_kind}", "traffic": traffic,
-                "algorithmic_bytes": gemm1_bytes, "ms": gemm1_ms}
+                "frac": achieved / hbm_peak, "peak_kind": f"of {peak_kind}", "traffic": None,
+                "traffic_note": "not captured in this run; ncu summaries of small cases are under profiles/",
+                "algorithmic_bytes": kernel_bytes, "ms": kernel_ms}
     # With many rows per expert the same kernel is bound by the tensor pipe instead.  The machine-readable peak file has a
     # bf16 figure only, so the FP8 denominator is the library's own probe of the MMA shape the kernel issues, run with
-    # pseudo-random operands (all-ones operands read ~10 % higher but no real data reaches that under the power cap).
-    kernel_flops = rows_recv * (2 * H * 2 * I if split else FLOP_PER_ROW)
+    # pseudo-random operands; the all-ones probe value and twice the measured bf16 figure are printed beside it.
     if rows_recv >= 200 * max(touched, 1):
-        fp8_peak = _lib.fp8_mma_peak_tflops(random_operands=True)
-        if kernel_flops / (fp8_peak * 1e12) > gemm1_bytes / (hbm_peak * 1e9):
-            tf = kernel_flops / (gemm1_ms * 1e-3) / 1e12
-            roofline = {"kernel": kernel_name, "bound": "tensor", "achieved": tf, "peak": fp8_peak, "unit": "TFLOP/s",
-                        "frac": tf / fp8_peak, "peak_kind": "of measured: own FP8 MMA probe with random operands, burst "
-                        "(MEASURED_PEAKS.json holds a bf16 figure only)", "traffic": traffic,
-                        "algorithmic_flops": kernel_flops, "algorithmic_bytes": gemm1_bytes, "ms": gemm1_ms}
+        fp8_rand = _lib.fp8_mma_peak_tflops(random_operands=True)
+        if kernel_flops / (fp8_rand * 1e12) > kernel_bytes / (hbm_peak * 1e9):
+            fp8_ones = _lib.fp8_mma_peak_tflops(random_operands=False)
+            bf16 = measured_bf16_tflops()
+            tf = kernel_flops / (kernel_ms * 1e-3) / 1e12
+            roofline = {"kernel": kernel_name, "bound": "tensor", "achieved": tf, "peak": fp8_rand, "unit": "TFLOP/s",
+                        "frac": tf / fp8_rand, "peak_kind": "of measured: own FP8 MMA probe with random operands, burst "
+                        "(MEASURED_PEAKS.json holds a bf16 figure only)",
+                        "fp8_peak_candidates_tflops": {"probe_random_operands": round(fp8_rand, 1), "probe_ones_operands": round(fp8_ones, 1),
+                                                       "twice_measured_bf16": None if bf16 is None else round(2 * bf16, 1)},
+                        "frac_of": {"probe_ones_operands": round(tf / fp8_ones, 4),
+                                    "twice_measured_bf16": None if bf16 is None else round(tf / (2 * bf16), 4)},
+                        "traffic": None, "traffic_note": "tensor-bound: see profiles/ for the pipe-utilisation capture",
+                        "algorithmic_flops": kernel_flops, "algorithmic_bytes": kernel_bytes, "ms": kernel_ms}
 
     total_rows = T * K * world
     value = T * world / (ms_step * 1e-3)
@@ -516,28 +664,69 @@ def main():
         "data": "synthetic",
         "config": {"workload": f"DSV4-Flash MoE layer: {E} experts top-{K} hidden {H} intermediate {I}, {T} tokens/rank, EP={world}, "
                                "uniform N(0,1)-logit routing, W8A8 channelwise", "tokens_per_rank": T, "ep": world,
-                   "l2": "weights streamed per step exceed L2 (no flush needed)", "variant": "staged" if staged else "fused"},
+                   "l2": "weights streamed per step exceed L2 (no flush needed)", "variant": variant},
         "fp8_tflops": total_rows * FLOP_PER_ROW / (ms_step * 1e-3) / 1e12,
         "e2e": {"value": T * world / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": e2e_ms},
+                "ms_per_step": e2e_ms, "copy_floor_ms": copy_floor_ms,
+                "over_floor": e2e_ms / max(copy_floor_ms, ms_step)},
         "gpu_launches": launches,
         "clocks": clocks,
         "roofline": roofline,
         "stage_ms": {k_: round(v, 4) for k_, v in acc.items()},
+        "parity": parity,
     }
+
+    if world > 1:
+        # ---- exposed communication: the step minus its all-local twin (this rank's experts only, the same token count and
+        #      top-k, one rank, no peer traffic), measured in the same run on every GPU at once
+        twin = megamoe.get_symm_buffer_for_mega_moe(None, e_loc, T, K, H, I)
+        twin._large_opt_3stage_mode, twin._staged_split = sb._large_opt_3stage_mode, sb._staged_split
+        g = torch.Generator(device=dev).manual_seed(77 + rank)
+        tw_, ti_ = torch.topk(torch.softmax(torch.randn((T, e_loc), generator=g, device=dev), dim=-1), K, dim=-1)
+        twin.x[:T].copy_(sb.x[:T]); twin.x_sf[:T].copy_(sb.x_sf[:T])
+        twin.topk_idx[:T].copy_(ti_); twin.topk_weights[:T].copy_((tw_ / tw_.sum(-1, keepdim=True)).float())
+        for _ in range(3):
+            megamoe.fp8_w8a8_mega_moe(y, l1, l2, twin)
+        barrier()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(args.steps):
+            megamoe.fp8_w8a8_mega_moe(y, l1, l2, twin)
+        t1.record()
+        barrier()
+        twin.check_status()
+        twin_ms = max_over_ranks(t0.elapsed_time(t1) / args.steps)
+        twin.destroy()
+        out["exposed_comm"] = {"all_local_twin_ms": twin_ms, "ms": ms_step - twin_ms, "frac_of_step": (ms_step - twin_ms) / ms_step}
+        # ---- NVLink: plain 16-byte stores of this library to one peer and to all peers (every rank at once), and the
+        #      remote bytes of the step over the time of the kernel(s) that move them
+        probe = nvlink_store_probe(dist, group, rank, world, dev, sb)
+        remote = rows_recv * (world - 1) / world
+        nvl = {"store_probe_gbs_per_direction": probe, "dispatch_bytes_out_per_rank": remote * (H + 16),
+               "combine_bytes_out_per_rank": remote * 2 * H}
+        if split:
+            nvl["dispatch_gbs"] = remote * (H + 16) / (max_over_ranks(acc["dispatch"]) * 1e-3) / 1e9
+            nvl["combine_gbs_over_gemm2"] = remote * 2 * H / (max_over_ranks(acc["gemm2"]) * 1e-3) / 1e9
+        else:
+            nvl["out_gbs_over_layer_kernel"] = remote * (3 * H + 16) / (kernel_ms * 1e-3) / 1e9
+        out["nvlink"] = nvl
+
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         threads = os.cpu_count() or 1
         n_exp = min(E, 128)                 # about 10 s of host work in all (three passes, best one reported)
         v, rows, secs = cpu_baseline(l1, l2, sb.x[:T], sb.x_sf[:T], idx, w, n_exp, threads, repeats=3)
         out["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": threads, "kind": "port",
+                               "gflops": round(rows * FLOP_PER_ROW / secs / 1e9, 1),
                                "sample": f"rows routed to the first {n_exp} of {E} experts ({rows} of {T * K} routed rows), "
                                          f"best of 3 passes, {secs:.1f} s each"}
     if rank == 0:
-        print(json.dumps(out))
+        print(json.dumps(out), flush=True)
     sb.destroy()
     if dist is not None:
         dist.barrier(group)
         dist.destroy_process_group()
+    if not parity["ok"]:
+        raise SystemExit("parity check failed: " + json.dumps(parity))
 
 
 if __name__ == "__main__":

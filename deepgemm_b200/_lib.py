@@ -15,8 +15,9 @@ LIB_PATH = os.path.join(_HERE, "libmegamoe_b200.so")
 SYM_NAMES = ["peer_ptrs", "signals", "runtime_num_tokens", "count_matrix", "x", "x_sf", "topk_idx", "topk_weights",
              "pool_x", "pool_meta", "combine", "pool_rows"]
 SCR_NAMES = ["status", "epoch", "plan", "block_counts", "dest_base", "expert_total", "expert_off", "mblock_expert",
-             "mblock_valid", "dest_row", "row_amax", "act_scale", "act_bf16", "act_fp8", "route_blocks"]
-MODE_STAGED, MODE_FUSED = 0, 1
+             "mblock_valid", "dest_row", "row_amax", "act_scale", "act_bf16", "act_fp8", "send_base", "send_list", "l1_done",
+             "l2_ready", "grid_sync", "route_blocks"]
+MODE_STAGED, MODE_FUSED, MODE_STAGED_SPLIT = 0, 1, 2
 MAX_RANKS = 16
 BLOCK_M = 128
 
@@ -40,6 +41,7 @@ _SIGNATURES = {
     "mm_m_grouped_fp8_gemm_nt_contiguous": (c_int, [c_void_p] * 6 + [c_int] * 4 + [c_void_p, c_void_p]),
     "mm_swiglu_quant_channelwise": (c_int, [c_void_p] * 6 + [c_int, c_int, c_int, c_float, c_void_p]),
     "mm_fp8_mma_peak_probe": (c_int, [c_int, c_int, c_int, c_void_p, c_void_p, POINTER(ctypes.c_double)]),
+    "mm_peer_store_probe": (c_int, [POINTER(c_uint64), c_int, c_int64, c_void_p]),
     "mm_router_topk_quant": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "mm_fp8_w8a8_mega_moe": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                      POINTER(c_uint64), c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
@@ -49,6 +51,7 @@ _SIGNATURES = {
     "mm_build_config": (c_int, [ctypes.c_char_p, c_int]),
     "mm_launch_count": (c_int64, []),
     "mm_fp8_w8a8_mega_moe_static": (c_int, [c_void_p] * 10 + [c_int] * 5 + [c_float, c_void_p]),
+    "mm_fp8_w8a8_mega_moe_static_status": (c_int, [c_void_p, POINTER(c_int32)]),
     "mm_set_stage_timing": (c_int, [c_int]),
     "mm_get_stage_times": (c_int, [POINTER(c_float), c_int]),
 }

@@ -244,6 +244,8 @@ int mm_scratch_layout(int R, int E, int T, int K, int H, int I, int64_t* offsets
         offsets[MM_SCR_MBLOCK_EXPERT] = L.mblock_expert; offsets[MM_SCR_MBLOCK_VALID] = L.mblock_valid;
         offsets[MM_SCR_DEST_ROW] = L.dest_row; offsets[MM_SCR_ROW_AMAX] = L.row_amax; offsets[MM_SCR_ACT_SCALE] = L.act_scale;
         offsets[MM_SCR_ACT_BF16] = L.act_bf16; offsets[MM_SCR_ACT_FP8] = L.act_fp8; offsets[MM_SCR_ROUTE_BLOCKS] = L.route_blocks;
+        offsets[MM_SCR_SEND_BASE] = L.send_base; offsets[MM_SCR_SEND_LIST] = L.send_list;
+        offsets[MM_SCR_L1_DONE] = L.l1_done; offsets[MM_SCR_L2_READY] = L.l2_ready; offsets[MM_SCR_GRID_SYNC] = L.grid_sync;
     }
     if (total_bytes) *total_bytes = L.total;
     return 0;
@@ -447,6 +449,22 @@ int mm_fp8_mma_peak_probe(int iters, int operands, int cta_pair, int* status_dev
     return 0;
 }
 
+int mm_peer_store_probe(const uint64_t* dst_ptrs, int n_dst, int64_t bytes_per_dst, void* stream_) {
+    MM_REQUIRE(dst_ptrs && n_dst > 0 && n_dst <= MM_MAX_RANKS && bytes_per_dst > 0 && bytes_per_dst % 512 == 0,
+               "mm_peer_store_probe: need 1..%d destinations and a positive multiple of 512 bytes", MM_MAX_RANKS);
+    mm::PeerStoreDsts d;
+    memset(&d, 0, sizeof(d));
+    for (int i = 0; i < n_dst; ++i) {
+        MM_REQUIRE(dst_ptrs[i] != 0 && (dst_ptrs[i] & 15) == 0, "mm_peer_store_probe: destinations must be 16-byte aligned");
+        d.ptr[i] = dst_ptrs[i];
+    }
+    int sms = 0;
+    if (int rc = sm_count(&sms)) return rc;
+    mm::peer_store_probe_kernel<<<sms * 8, 256, 0, static_cast<cudaStream_t>(stream_)>>>(d, n_dst, bytes_per_dst / 16);
+    MM_LAUNCHED();
+    return 0;
+}
+
 int mm_router_topk_quant(const void* x_bf16, const float* router_logits, int num_tokens, int E, int K, int H, void* x_fp8,
                          float* x_sf, int64_t* topk_idx, float* topk_weights, void* stream_) {
     MM_REQUIRE(num_tokens >= 0 && E > 0 && E <= MM_MAX_EXPERTS && K > 0 && K <= MM_MAX_TOPK && K <= E && H > 0 && H % 8 == 0,
@@ -478,7 +496,7 @@ int mm_fp8_w8a8_mega_moe(void* y, const void* w1, const float* s1, const void* w
     MM_REQUIRE(num_tokens >= 0 && num_tokens <= T_max, "too many tokens");
     MM_REQUIRE(peer_ptrs[rank] == reinterpret_cast<uint64_t>(sym_base), "peer_ptrs[rank] must be the local buffer");
     MM_REQUIRE(!isnan(activation_clamp) && activation_clamp > 0.0f, "activation_clamp must be positive (+inf for none)");
-    MM_REQUIRE(mode == MM_MODE_STAGED || mode == MM_MODE_FUSED, "unknown mode");
+    MM_REQUIRE(mode == MM_MODE_STAGED || mode == MM_MODE_FUSED || mode == MM_MODE_STAGED_SPLIT, "unknown mode");
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
 
     mm::RouteParams rp;
@@ -493,8 +511,8 @@ int mm_fp8_w8a8_mega_moe(void* y, const void* w1, const float* s1, const void* w
     rp.runtime_num_tokens = runtime_num_tokens;
     rp.stats = stats;
     rp.barrier_timeout_ns = (uint64_t)g_barrier_ms.load() * 1000000ull;
-    // with a device-side token count every block that could own a route must run
-    const int64_t tokens_bound = runtime_num_tokens ? T_max : num_tokens;
+    // a device-side token count is clamped to num_tokens (the rows of y), so num_tokens bounds the routes in both modes
+    const int64_t tokens_bound = num_tokens;
     int route_blocks = (int)((tokens_bound * K + MM_ROUTE_CHUNK - 1) / MM_ROUTE_CHUNK);
     if (route_blocks < 1) route_blocks = 1;
     rp.cl.route_blocks = route_blocks;   // blocks whose histogram rows are live in this call
@@ -523,7 +541,7 @@ int mm_fp8_w8a8_mega_moe(void* y, const void* w1, const float* s1, const void* w
     g1.timeout_ns = (uint64_t)g_pipe_ms.load() * 1000000ull;
     for (int r = 0; r < R; ++r) g1.peers[r] = peer_ptrs[r];
     g1.combine_off = rp.sl.combine;
-    g1.T = T_max; g1.H = H;
+    g1.T = T_max; g1.H = H; g1.R = R; g1.K = K;
     g1.act_bf16 = reinterpret_cast<__nv_bfloat16*>(sc + rp.cl.act_bf16);
     g1.row_amax = reinterpret_cast<unsigned int*>(sc + rp.cl.row_amax);
     g1.act_scale = reinterpret_cast<const float*>(sc + rp.cl.act_scale);
@@ -538,19 +556,22 @@ int mm_fp8_w8a8_mega_moe(void* y, const void* w1, const float* s1, const void* w
     fp.g1 = g1;
     fp.g2 = g2;
     fp.y = static_cast<__nv_bfloat16*>(y);
+    fp.plan = reinterpret_cast<int*>(sc + rp.cl.plan);
     fp.l1_done = reinterpret_cast<int*>(sc + rp.cl.l1_done);
     fp.l2_ready = reinterpret_cast<int*>(sc + rp.cl.l2_ready);
     fp.grid_sync = reinterpret_cast<int*>(sc + rp.cl.grid_sync);
+    fp.send_list = reinterpret_cast<const int4*>(sc + rp.cl.send_list);
     fp.act_fp8 = sc + rp.cl.act_fp8;
     fp.act_scale_w = reinterpret_cast<float*>(sc + rp.cl.act_scale);
     // a wave holds enough GEMM1 tiles for about two rounds over the SMs, so its requantisation is done when its GEMM2 starts
     fp.wave_mblocks = (2 * sms + g1.n_blocks - 1) / g1.n_blocks;
-    if (const char* v = getenv("MEGAMOE_WAVE_MBLOCKS")) { const int w = atoi(v); fp.wave_mblocks = w > 0 ? w : (1 << 28); }   // tuning aid
+    static const int wave_override = [] { const char* v = getenv("MEGAMOE_WAVE_MBLOCKS"); return v ? atoi(v) : 0; }();   // tuning aid
+    if (wave_override != 0) fp.wave_mblocks = wave_override > 0 ? wave_override : (1 << 28);
+    static const int helper_policy = [] { const char* v = getenv("MEGAMOE_HELPER_POLICY"); return v ? atoi(v) : 2; }();   // tuning aid
+    fp.policy = helper_policy;
     void* fused_args[] = {&tm_pool, &tm_w1, &tm_act, &tm_w2, &fp};
 
     if (mode == MM_MODE_FUSED) {
-        MM_REQUIRE(tokens_bound * K <= mm::kFusedMaxRoutes,
-                   "the fused variant holds at most %d routes (tokens x top-k) per rank; use the staged variant", mm::kFusedMaxRoutes);
         if (int rc = stage_begin(stream)) return rc;
         // cooperative launch: all CTAs must be resident because they wait on one another
         MM_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(mm::mega_moe_fused_kernel), dim3(sms), dim3(mm::kFusedThreads),
@@ -560,10 +581,10 @@ int mm_fp8_w8a8_mega_moe(void* y, const void* w1, const float* s1, const void* w
         return 0;
     }
 
-    // Staged variant: GEMM1, requantisation and GEMM2 are separate launches.  Measured on one B200 this beats running them as
-    // one cooperative kernel in wave order (gemm_only mode of the fused kernel, MEGAMOE_STAGED_MERGED=1) by 5-13 % at
-    // 4096-8192 tokens: the requantisation tiles and per-m-block dependency polls cost more than the launch gaps.
-    static const bool split_gemms = [] { const char* v = getenv("MEGAMOE_STAGED_MERGED"); return !(v && v[0] == '1'); }();
+    // Staged variants: routing as small kernels, then
+    //   MM_MODE_STAGED        the layer kernel in gemm_only mode: NVLink push, GEMM1, requantisation and GEMM2 tiles in one
+    //                         launch, so that the transfers overlap the tensor work expert by expert;
+    //   MM_MODE_STAGED_SPLIT  dispatch, a cross-rank barrier, GEMM1, requantisation and GEMM2 as separate launches.
     if (int rc = stage_begin(stream)) return rc;
 #define MM_STAGE(id) do { MM_LAUNCHED(); if (int rc_ = stage_end(id, stream)) return rc_; } while (0)
     mm::route_count_kernel<<<route_blocks, MM_ROUTE_CHUNK, 0, stream>>>(rp);
@@ -572,22 +593,26 @@ int mm_fp8_w8a8_mega_moe(void* y, const void* w1, const float* s1, const void* w
     MM_STAGE(MM_STAGE_ROUTE_EXCHANGE);
     mm::route_plan_kernel<<<1, 1024, 0, stream>>>(rp);
     MM_STAGE(MM_STAGE_ROUTE_PLAN);
+    if (mode == MM_MODE_STAGED) {
+        mm::send_plan_kernel<<<route_blocks, MM_ROUTE_CHUNK, 0, stream>>>(rp);
+        MM_STAGE(MM_STAGE_DISPATCH);
+        fp.gemm_only = 1;
+        MM_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(mm::mega_moe_fused_kernel), dim3(sms), dim3(mm::kFusedThreads),
+                                            fused_args, mm::kGemmSmemBytes, stream));
+        MM_STAGE(MM_STAGE_FUSED);
+        // Leave the per-m-block dependency counters zero for the next call.  l1_done, l2_ready and grid_sync are adjacent;
+        // the arrival counters live in the symmetric buffer: peers bump them again only after every rank has entered its
+        // next call (they wait for its route counts first), which on this stream comes after this memset.
+        const int64_t n_mb = rp.sl.pool_rows / MM_BLOCK_M;
+        MM_CUDA(cudaMemsetAsync(sc + rp.cl.l1_done, 0, (size_t)(rp.cl.grid_sync + 32 - rp.cl.l1_done), stream));
+        MM_CUDA(cudaMemsetAsync(rp.sym + rp.sl.pool_arrive, 0, (size_t)(n_mb + 1) * sizeof(int), stream));
+    } else {
     mm::dispatch_kernel<<<route_blocks, mm::MM_DISPATCH_THREADS, 0, stream>>>(rp);
     MM_STAGE(MM_STAGE_DISPATCH);
     if (R > 1) {
         mm::rank_barrier_kernel<<<1, 32, 0, stream>>>(rp, MM_BAR_DISPATCH);
         MM_STAGE(MM_STAGE_BARRIER_DISPATCH);
     }
-    if (!split_gemms) {
-        fp.gemm_only = 1;
-        MM_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(mm::mega_moe_fused_kernel), dim3(sms), dim3(mm::kFusedThreads),
-                                            fused_args, mm::kGemmSmemBytes, stream));
-        MM_STAGE(MM_STAGE_FUSED);
-        // leave the per-m-block dependency counters zero for the next call (l1_done and l2_ready are adjacent regions)
-        const int64_t n_mb = rp.sl.pool_rows / MM_BLOCK_M;
-        MM_CUDA(cudaMemsetAsync(sc + rp.cl.l1_done, 0, (size_t)(rp.cl.l2_ready - rp.cl.l1_done + n_mb * 4), stream));
-        MM_CUDA(cudaMemsetAsync(sc + rp.cl.grid_sync + 2 * sizeof(int), 0, sizeof(int), stream));
-    } else {
     // CTA-pair GEMMs (two m-blocks of one expert share each weight tile).  Measured on B200 (hidden 4096, intermediate
     // 2048): with 192 rows per expert -- two m-blocks, the regime between HBM-bound and tensor-bound, where the one-CTA
     // kernel streams every weight tile once from HBM and once more from L2 -- they take 10 % off both GEMMs; with 384 rows
@@ -595,7 +620,7 @@ int mm_fp8_w8a8_mega_moe(void* y, const void* w1, const float* s1, const void* w
     // So they are used when an expert is expected to hold two m-blocks; MEGAMOE_GEMM_PAIR=0/1 overrides.
     const int64_t expected_routes = (int64_t)tokens_bound * K;        // per local expert: expected_routes / E_loc
     bool pair_gemms = expected_routes > (int64_t)144 * E_loc && expected_routes <= (int64_t)256 * E_loc && sms >= 2;
-    if (const char* v = getenv("MEGAMOE_GEMM_PAIR")) pair_gemms = v[0] == '1' && sms >= 2;
+    if (const char* v = getenv("MEGAMOE_GEMM_PAIR")) pair_gemms = v[0] == '1' && sms >= 2;   // read per call: tests switch it
     CUtensorMap tm_w1h, tm_w2h;
     if (pair_gemms) {
         if (int rc = tensor_map_2d(w1, 128, (uint64_t)E_loc * (I / 128) * (H / 128) * 256, 128, &tm_w1h)) return rc;
@@ -612,7 +637,7 @@ int mm_fp8_w8a8_mega_moe(void* y, const void* w1, const float* s1, const void* w
     else mm::grouped_gemm_kernel<0><<<sms, mm::kGemmThreads, mm::kGemmSmemBytes, stream>>>(tm_pool, tm_w1, g1);
     MM_STAGE(MM_STAGE_GEMM1);
     mm::requant_kernel<<<sms * 4, 256, 0, stream>>>(g1.act_bf16, I, g1.plan, g1.mblock_valid, g1.row_amax,
-                                                   reinterpret_cast<float*>(sc + rp.cl.act_scale), sc + rp.cl.act_fp8);
+                                                   reinterpret_cast<float*>(sc + rp.cl.act_scale), sc + rp.cl.act_fp8, g1.status);
     MM_STAGE(MM_STAGE_REQUANT);
     if (pair_gemms) mm::grouped_gemm_pair_kernel<1><<<pair_grid, mm::kGemmThreads, mm::kPairSmemBytes, stream>>>(tm_act, tm_w2h, g2);
     else mm::grouped_gemm_kernel<1><<<sms, mm::kGemmThreads, mm::kGemmSmemBytes, stream>>>(tm_act, tm_w2, g2);
@@ -623,7 +648,7 @@ int mm_fp8_w8a8_mega_moe(void* y, const void* w1, const float* s1, const void* w
         MM_STAGE(MM_STAGE_BARRIER_COMBINE);
     }
     mm::combine_reduce_kernel<<<sms * 8, 256, 0, stream>>>(rp.sym, rp.sl, E, T_max, K, H, num_tokens, runtime_num_tokens,
-                                                          static_cast<__nv_bfloat16*>(y));
+                                                          static_cast<__nv_bfloat16*>(y), g1.status);
     MM_STAGE(MM_STAGE_REDUCE);
 #undef MM_STAGE
     return 0;

@@ -1,26 +1,38 @@
-// The whole layer as ONE persistent, warp-specialised kernel (small and medium token counts).
+// The layer's compute phase -- and, in MM_MODE_FUSED, the whole layer -- as ONE persistent, warp-specialised kernel.
 //
 // Replaces mega_moe_multirank_persistent_w8a8_channelwise_kernel
 // (deep_gemm/include/deep_gemm/impls/mega_moe_dcu.cuh:259-765).  One CTA per SM, launched cooperatively so that all
-// CTAs are resident (they wait on one another).  Timeline of a CTA:
-//   1. every CTA histograms this rank's routes in shared memory; CTA 0 publishes the count vector to all ranks;
-//   2. wait (bounded) for all ranks' count vectors, derive the plan (totals, pool offsets, m-block table) locally;
-//   3. push this CTA's share of the routed rows to the owners' pools over NVLink; every row bumps the owner's per-m-block
-//      arrival counter (red.release.sys);
-//   4. tile loop, round-robin over CTAs, with the same TMA / MMA / epilogue warp roles as grouped_gemm_kernel.  The
-//      m-blocks are grouped in waves; GEMM1 tiles of wave k+2, requantisation tiles of wave k and GEMM2 tiles of wave k
-//      alternate (see WaveOrder), so the tensor-bound GEMM1 work overlaps the NVLink-bound combine stores of GEMM2.
-//      Dependencies are per m-block, not global barriers:
-//        - GEMM1 tile: weights start streaming at once; the token operand waits for the m-block's arrival counter; each
-//          epilogue warp counts its stored share in l1_done[m-block];
-//        - requantisation tile (epilogue warps only, the MMA pipeline runs on): waits for all GEMM1 tiles of the m-block,
-//          turns its bf16 rows into e4m3 (the channelwise scale needs the whole row) and sets l2_ready[m-block];
-//        - GEMM2 tile: the activation operand waits for l2_ready[m-block] == 4; its epilogue stores to the source rank;
-//   5. grid barrier -> CTA 0 tells every rank "my combine stores are done"; wait for all ranks; top-k reduce; clean up.
-// Every wait is for tiles earlier in the tile order (or for dispatch), and every role of a CTA walks its tiles in order,
-// so the waits cannot form a cycle.  Every wait is bounded and ends in a status code, never in a hang.
-// gemm_only = 1 runs step 4 alone, between the staged routing / dispatch launches and the staged combine barrier and
-// reduce launches (any token count); the host resets the dependency counters afterwards.
+// CTAs are resident (they wait on one another).  Warp roles of a CTA (384 threads):
+//   warp 0      TMA producer: streams weight tiles and pool / activation tiles into the operand ring;
+//   warp 1      MMA issuer: tcgen05.mma into two TMEM accumulators;
+//   warps 2-3   helpers: (a) push routed rows to the owners' receive pools over NVLink, (b) requantise finished m-blocks;
+//   warps 4-11  epilogue: TMEM -> scales / SwiGLU -> global memory (GEMM2: straight into the source rank's combine buffer).
+//
+// Two entry modes.
+//   gemm_only = 0 (MM_MODE_FUSED, small token counts, one launch per layer call):
+//     1. every CTA histograms ALL of this rank's routes in shared memory and counts those before its own contiguous
+//        share; CTA 0 publishes the count vector to all ranks;
+//     2. bounded wait for all ranks' count vectors; every CTA derives the plan (totals, pool offsets, m-block table);
+//     3. all warps push the CTA's share of the rows (row = base of the expert + routes before the share + rank inside
+//        the share) and bump the owner's per-m-block arrival counters;
+//     4. the tile loop below;  5. grid barrier, cross-rank "combine stores done" barrier;  6. top-k reduce;  7. clean-up.
+//   gemm_only = 1 (MM_MODE_STAGED, any token count): the routing kernels of route.cuh made the plan, the destination row
+//     of every route and a SEND LIST (this rank's valid routes ordered by local expert index, then owner); the kernel
+//     runs step 4 only, and its helper warps first walk the send list -- so all ranks fill expert 0 of every owner first,
+//     then expert 1, ... and an owner's GEMM1 tiles start as soon as their m-block has arrived, while later experts'
+//     rows are still crossing NVLink.  The combine barrier, the reduce and the counter reset are launches after it.
+//
+// Step 4, the tile loop: m-blocks are grouped in waves; with G1(k) / G2(k) = all GEMM1 / GEMM2 tiles of wave k the
+// order is  G1(0), G1(1), [G1(2), G2(0)], [G1(3), G2(1)], ..., G2(n-1)  (round-robin over CTAs), so the tensor-bound
+// GEMM1 work overlaps the NVLink-bound combine stores of GEMM2.  Dependencies are per m-block, never global barriers:
+//   - GEMM1 tile: weights start streaming at once; the token operand waits for arrive[m-block] == valid rows; each
+//     epilogue warp counts its stored share in l1_done[m-block];
+//   - requantisation unit (a 32-row quarter of an m-block, claimed in order by the helper warps of ALL CTAs): waits for
+//     every GEMM1 tile of the m-block (the channelwise scale needs the whole row), converts bf16 -> e4m3, bumps l2_ready;
+//   - GEMM2 tile: the activation operand waits for l2_ready[m-block] == 4.
+// A tile only ever waits for work that belongs to tiles earlier in the order (or for pushes, which wait for nothing),
+// every role walks its items in order and all CTAs are resident, so the waits cannot form a cycle.  Every wait is
+// bounded and ends in a status code, never in a hang.
 #pragma once
 #include "gemm.cuh"
 #include "misc.cuh"
@@ -28,36 +40,48 @@
 
 namespace mm {
 
-constexpr int kFusedMaxRoutes = 4096;      // routes of this rank held in shared memory (tokens * top-k)
-constexpr int kFusedThreads = kGemmThreads;
+constexpr int kHelperWarps = 2;
+constexpr int kFusedFirstEpilogueWarp = 2 + kHelperWarps;                    // a multiple of 4: warp & 3 == TMEM lane quarter
+constexpr int kFusedThreads = (kFusedFirstEpilogueWarp + kEpilogueWarps) * 32;
+constexpr int kPushChunk = 8;             // rows a helper warp claims, pushes and signals at a time
+static_assert(kFusedFirstEpilogueWarp % 4 == 0, "epilogue warps must start at a multiple of four");
+
+// words of the `plan` array in the scratch buffer (written by route_plan_kernel or by this kernel's step 2)
+enum { MM_PLAN_MBLOCKS = 0, MM_PLAN_ROWS_PADDED = 1, MM_PLAN_PAIRS = 2, MM_PLAN_SEND = 3, MM_PLAN_ROWS_EXPECTED = 6 };
+// words of the `grid_sync` array: all zero between calls (this kernel's last step, or a memset after a gemm_only launch)
+enum { MM_SYNC_CTAS = 0, MM_SYNC_CALLS = 1, MM_SYNC_UNITS_DONE = 2, MM_SYNC_PUSH_HEAD = 3, MM_SYNC_REQUANT_HEAD = 4 };
 
 struct FusedParams {
     RouteParams rp;
     GemmParams g1, g2;
     __nv_bfloat16* y;
-    int* l1_done;          // [4 * m-blocks]
-    int* l2_ready;         // [m-blocks]
-    int* grid_sync;        // [0] CTA arrivals (monotonic), [1] fused calls completed
+    int* plan;             // [8] see MM_PLAN_*
+    int* l1_done;          // [m-blocks] epilogue warps that stored their share of a GEMM1 tile of the m-block
+    int* l2_ready;         // [m-blocks] requantised quarters of the m-block
+    int* grid_sync;        // [8] see MM_SYNC_*
+    const int4* send_list; // [valid routes] {route, pool row, owner rank, token} in send order (gemm_only)
     uint8_t* act_fp8;      // [pool_rows][I]
     float* act_scale_w;    // writable alias of g2.act_scale
-    int wave_mblocks;      // m-blocks per wave of the tile order (see decode_tile)
-    int gemm_only;         // 1: routing and dispatch were done by the staged kernels (and a dispatch barrier); start at the tile loop
+    int wave_mblocks;      // m-blocks per wave of the tile order
+    int gemm_only;         // 1: routing was done by the staged kernels; start at the tile loop and stop after it
+    int policy;            // tuning switches: bit 0 = both helper warps push even with several ranks,
+                           //                  bit 1 = epilogue warps help pushing until their first accumulator is complete
 };
 
-// shared-memory scratch of the routing phases, aliased onto the (not yet used) operand ring
+// shared-memory scratch of the routing steps, aliased onto the (not yet used) operand ring
 struct FusedRouteSmem {
-    int hist[MM_MAX_EXPERTS];        // this rank's routes per expert
+    int hist[MM_MAX_EXPERTS];        // this rank's valid routes per expert
+    int before[MM_MAX_EXPERTS];      // ... of them, routes that come before this CTA's share (then: running count inside it)
     int tot[MM_MAX_EXPERTS];         // rows received by each expert (all ranks)
     int dest[MM_MAX_EXPERTS];        // first pool row on the owner for this rank's routes to the expert
     int off[MM_MAX_EXPERTS];         // pool offset of the expert on its owner
-    short expert[kFusedMaxRoutes];   // expert of each local route, -1 = invalid
 };
 static_assert(sizeof(FusedRouteSmem) <= kStages * kStageBytes, "routing scratch must fit in the operand ring");
 
 // Spin (bounded) until *flag - target >= 0.  `sys` selects system scope (flag written by another GPU).
 // Gives up when the time budget is spent or another wait of the grid already failed (status code set).
 __device__ __forceinline__ bool wait_flag_ge(const int* flag, int target, bool sys, const int* status_code, uint64_t timeout_ns,
-                                             int* observed) {
+                                             int* observed, unsigned sleep_ns = 40) {
     int v = sys ? ld_acquire_sys(flag) : ld_acquire_gpu(flag);
     if (v - target >= 0) { *observed = v; return true; }
     const uint64_t t0 = global_timer_ns();
@@ -68,42 +92,166 @@ __device__ __forceinline__ bool wait_flag_ge(const int* flag, int target, bool s
         if ((++it & 15u) == 0u) {
             if (ld_acquire_gpu(status_code) != 0 || global_timer_ns() - t0 > timeout_ns) { *observed = v; return false; }
         }
-        __nanosleep(40);
+        __nanosleep(sleep_ns);
     }
 }
 
-// Position of a tile index in the wave order of the kernel below.  A CTA's tile indices grow, so seek() only moves forward.
+// Position of a tile index in the wave order.  A CTA's tile indices grow, so seek() only moves forward.
 struct WaveOrder {
-    enum { kG1 = 0, kRequant = 1, kG2 = 2 };
+    enum { kG1 = 0, kG2 = 1 };
     int n_waves, wave_m, num_mblocks, nb1, nb2;
     int g, base, size, kind, wave;
     __device__ WaveOrder(int num_mblocks_, int wave_m_, int nb1_, int nb2_)
         : n_waves((num_mblocks_ + wave_m_ - 1) / wave_m_), wave_m(wave_m_), num_mblocks(num_mblocks_), nb1(nb1_), nb2(nb2_),
           g(0), base(0) { set(); }
     __device__ __forceinline__ int wave_mblocks(int w) const { return w < n_waves ? min(wave_m, num_mblocks - w * wave_m) : 0; }
-    __device__ __forceinline__ void set() {      // groups: G1(0), G1(1), then triples R(k), G1(k+2), G2(k)
+    __device__ __forceinline__ void set() {      // groups: G1(0), G1(1), then pairs G1(k+2), G2(k)
         if (g < 2) { kind = kG1; wave = g; }
         else {
-            const int k = (g - 2) / 3, j = (g - 2) - 3 * k;
-            kind = j == 0 ? kRequant : (j == 1 ? kG1 : kG2);
-            wave = j == 1 ? k + 2 : k;
+            const int k = (g - 2) >> 1, j = (g - 2) & 1;
+            kind = j == 0 ? kG1 : kG2;
+            wave = j == 0 ? k + 2 : k;
         }
-        size = wave_mblocks(wave) * (kind == kG1 ? nb1 : (kind == kRequant ? 1 : nb2));
+        size = wave_mblocks(wave) * (kind == kG1 ? nb1 : nb2);
     }
-    // tile -> (kind, m-block, n-block); the caller guarantees tile < num_mblocks * (nb1 + 1 + nb2)
+    // tile -> (kind, m-block, n-block); the caller guarantees tile < num_mblocks * (nb1 + nb2)
     __device__ __forceinline__ void seek(int tile, int& kind_out, int& mb, int& nb) {
         while (tile >= base + size) { base += size; ++g; set(); }
         const int r = tile - base;
-        const int per = kind == kG1 ? nb1 : (kind == kRequant ? 1 : nb2);
+        const int per = kind == kG1 ? nb1 : nb2;
         mb = wave * wave_m + r / per;
         nb = r - (r / per) * per;
         kind_out = kind;
     }
 };
 
+// Copy up to two FP8 rows of `H` bytes (16-byte vectors, all their loads in flight together) -- the data part of a push.
+__device__ __forceinline__ void push_two_rows(const uint8_t* src0, uint8_t* dst0, const uint8_t* src1, uint8_t* dst1, int H, int lane) {
+    const int nvec = H / 16;
+    for (int v0 = 0; v0 < nvec; v0 += 32 * 8) {
+        uint4 a[8], b[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const int v = v0 + k * 32 + lane;
+            if (v < nvec) {
+                a[k] = __ldg(reinterpret_cast<const uint4*>(src0) + v);
+                if (src1) b[k] = __ldg(reinterpret_cast<const uint4*>(src1) + v);
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const int v = v0 + k * 32 + lane;
+            if (v < nvec) {
+                reinterpret_cast<uint4*>(dst0)[v] = a[k];
+                if (src1) reinterpret_cast<uint4*>(dst1)[v] = b[k];
+            }
+        }
+    }
+}
+
+// One chunk of the send list (helper warps, gemm_only): copy up to kPushChunk rows into their owners' receive pools, write
+// their metadata, then -- warp barrier, one system-scope fence -- count one arrival per row on the owner (per m-block and
+// in total).
+__device__ __forceinline__ void push_chunk(const FusedParams& fp, int j0, int n_send, int lane) {
+    const RouteParams& rp = fp.rp;
+    const float* tw = reinterpret_cast<const float*>(rp.sym + rp.sl.topk_weights);
+    const float* x_sf = reinterpret_cast<const float*>(rp.sym + rp.sl.x_sf);
+    const uint8_t* x = rp.sym + rp.sl.x;
+    const int arrive_total_slot = static_cast<int>(rp.sl.pool_rows / MM_BLOCK_M);
+    const int n = min(kPushChunk, n_send - j0);
+    // lane j < n describes row j of the chunk
+    int route = -1, row = -1, owner = 0, token = 0;
+    if (lane < n) {
+        const int4 rec = __ldcg(fp.send_list + j0 + lane);
+        route = rec.x; row = rec.y; owner = rec.z; token = rec.w;
+        if (row < 0 || owner < 0 || owner >= rp.R || token < 0 || token >= rp.T) row = -1;
+    }
+    for (int j = 0; j < n; j += 2) {
+        const int row0 = __shfl_sync(0xffffffffu, row, j), tok0 = __shfl_sync(0xffffffffu, token, j);
+        const int own0 = __shfl_sync(0xffffffffu, owner, j);
+        const int row1 = __shfl_sync(0xffffffffu, row, j + 1), tok1 = __shfl_sync(0xffffffffu, token, j + 1);
+        const int own1 = __shfl_sync(0xffffffffu, owner, j + 1);
+        const bool has0 = row0 >= 0, has1 = j + 1 < n && row1 >= 0;
+        const uint8_t* s0 = x + static_cast<int64_t>(tok0) * rp.H;
+        uint8_t* d0 = reinterpret_cast<uint8_t*>(rp.peers[own0]) + rp.sl.pool_x + static_cast<int64_t>(row0) * rp.H;
+        const uint8_t* s1 = x + static_cast<int64_t>(tok1) * rp.H;
+        uint8_t* d1 = reinterpret_cast<uint8_t*>(rp.peers[own1]) + rp.sl.pool_x + static_cast<int64_t>(row1) * rp.H;
+        if (has0) push_two_rows(s0, d0, has1 ? s1 : nullptr, d1, rp.H, lane);
+        else if (has1) push_two_rows(s1, d1, nullptr, nullptr, rp.H, lane);
+    }
+    if (row >= 0) {
+        MmPoolMeta m;
+        m.x_scale = x_sf[token];
+        m.route_weight = tw[route];
+        m.src_token = token;
+        m.src_info = (rp.rank << 8) | (route - token * rp.K);
+        *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(rp.peers[owner]) + rp.sl.pool_meta +
+                                  static_cast<int64_t>(row) * sizeof(MmPoolMeta)) = *reinterpret_cast<uint4*>(&m);
+    }
+    __syncwarp();
+    __threadfence_system();
+    if (row >= 0) {
+        int* arr = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(rp.peers[owner]) + rp.sl.pool_arrive);
+        asm volatile("red.relaxed.sys.global.add.s32 [%0], 1;" ::"l"(arr + row / MM_BLOCK_M) : "memory");
+        asm volatile("red.relaxed.sys.global.add.s32 [%0], 1;" ::"l"(arr + arrive_total_slot) : "memory");
+    }
+}
+
+// One requantisation unit (helper warps): rows [32q, 32q+32) of m-block mb, bf16 -> e4m3 with one scale per row,
+// s2 = max(amax / 448, 1e-4) (deep_gemm/include/deep_gemm/impls/mega_moe_dcu_tiles.cuh:672-733), then count the quarter
+// towards l2_ready[mb].  The caller has seen, with an acquire load, that every GEMM1 tile of the m-block is stored.
+__device__ __forceinline__ void requant_unit(const FusedParams& fp, int u, int lane) {
+    const GemmParams& g1 = fp.g1;
+    const int inter = g1.n_out, vecs = inter / 8;
+    const int mb = u >> 2, r_lo = (u & 3) * 32;
+    const int r_hi = min(r_lo + 32, g1.mblock_valid[mb]);
+    for (int r = r_lo; r < r_hi; r += 2) {
+        uint4 buf[2][8];
+        float inv[2], sc2[2];
+#pragma unroll
+        for (int u2 = 0; u2 < 2; ++u2) {
+            const int64_t prow = static_cast<int64_t>(mb) * kBlockM + min(r + u2, r_hi - 1);
+            const float amax = __uint_as_float(__ldcg(g1.row_amax + prow));
+            sc2[u2] = fmaxf(__fdiv_rn(amax, 448.0f), 1.0e-4f);
+            inv[u2] = __fdiv_rn(1.0f, sc2[u2]);
+            const uint4* src = reinterpret_cast<const uint4*>(g1.act_bf16 + prow * inter);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) { const int v = k * 32 + lane; if (v < vecs) buf[u2][k] = __ldcg(src + v); }
+        }
+#pragma unroll
+        for (int u2 = 0; u2 < 2; ++u2) {
+            if (r + u2 >= r_hi) continue;
+            const int64_t prow = static_cast<int64_t>(mb) * kBlockM + r + u2;
+            const uint4* src = reinterpret_cast<const uint4*>(g1.act_bf16 + prow * inter);
+            uint2* dst = reinterpret_cast<uint2*>(fp.act_fp8 + prow * inter);
+            for (int v0 = 0; v0 < vecs; v0 += 32 * 8) {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const int v = v0 + k * 32 + lane;
+                    if (v < vecs) {
+                        const uint4 d = (v0 == 0) ? buf[u2][k] : __ldcg(src + v);
+                        uint2 o;
+                        o.x = pack4_e4m3(bf16_lo(d.x) * inv[u2], bf16_hi(d.x) * inv[u2], bf16_lo(d.y) * inv[u2], bf16_hi(d.y) * inv[u2]);
+                        o.y = pack4_e4m3(bf16_lo(d.z) * inv[u2], bf16_hi(d.z) * inv[u2], bf16_lo(d.w) * inv[u2], bf16_hi(d.w) * inv[u2]);
+                        dst[v] = o;
+                    }
+                }
+            }
+            if (lane == 0) { fp.act_scale_w[prow] = sc2[u2]; g1.row_amax[prow] = 0u; }
+        }
+    }
+    __syncwarp();
+    if (lane == 0) {
+        __threadfence();
+        red_release_gpu_add(fp.l2_ready + mb, 1);     // GEMM2 producers wait for 4
+        red_release_gpu_add(fp.grid_sync + MM_SYNC_UNITS_DONE, 1);
+    }
+}
+
 __global__ void __launch_bounds__(kFusedThreads, 1)
 mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_constant__ CUtensorMap tm_w1,
-                      const __grid_constant__ CUtensorMap tm_act, const __grid_constant__ CUtensorMap tm_w2, FusedParams fp) {
+                      const __grid_constant__ CUtensorMap tm_act, const __grid_constant__ CUtensorMap tm_w2,
+                      const __grid_constant__ FusedParams fp) {
     const RouteParams& rp = fp.rp;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const uint32_t smem_base = smem_u32(smem_raw);
@@ -124,13 +272,15 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
     uint8_t* tail = smem_gen + kStages * kStageBytes + kStagingBytes + kScaleBytes + 8 * (2 * kStages + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tail);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail + 8);
-    int* s_misc = reinterpret_cast<int*>(tail + 16);       // [0] number of m-blocks, [1] ok flag of block-wide waits, [2] rows to receive, [3] requant-owner flag
+    int* s_misc = reinterpret_cast<int*>(tail + 16);       // [0] number of m-blocks, [1] ok flag of block-wide waits, [2] rows to receive,
+                                                           // [4] leading tiles of this CTA whose dependency the scout has confirmed
     FusedRouteSmem& rs = *reinterpret_cast<FusedRouteSmem*>(smem_gen);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tid = threadIdx.x, nthr = blockDim.x;
     // timeline of CTA 0 (tenths of a microsecond since kernel entry) in the spare status words, for tuning:
-    // [5] plan ready, [6] rows pushed, [7] producer done, [8] MMA done, [9] epilogue done, [10] all ranks done, [11] reduced
+    // [5] plan ready, [6] rows pushed, [7] producer done, [8] MMA done, [9] epilogue done, [10] all ranks done, [11] reduced,
+    // [12] helper pushes done, [13] helper requantisation done, [14] / [15] producer's own polling for GEMM1 arrivals / GEMM2 requantisation
     const uint64_t t_entry = global_timer_ns();
     auto stamp = [&](int slot) { if (blockIdx.x == 0) status[slot] = static_cast<int>((global_timer_ns() - t_entry) / 100); };
 
@@ -139,7 +289,7 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
         for (int s = 0; s < kStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
         for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), kEpilogueWarps); }
         *abort_flag = 0;
-        s_misc[0] = 0; s_misc[1] = 1; s_misc[2] = 0;
+        s_misc[0] = 0; s_misc[1] = ld_acquire_gpu(status) == 0 ? 1 : 0; s_misc[2] = 0; s_misc[4] = 0;
         fence_barrier_init();
         prefetch_tensormap(&tm_pool); prefetch_tensormap(&tm_w1); prefetch_tensormap(&tm_act); prefetch_tensormap(&tm_w2);
     }
@@ -149,22 +299,26 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
     const int fused_calls = fp.grid_sync[1];
     const int n_tokens = route_num_tokens(rp);
     const int n_routes = n_tokens * rp.K;
-    for (int e = tid; e < rp.E; e += nthr) rs.hist[e] = 0;
+    for (int e = tid; e < rp.E; e += nthr) { rs.hist[e] = 0; rs.before[e] = 0; }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    const int arrive_total_slot = static_cast<int>(rp.sl.pool_rows / MM_BLOCK_M);   // last word of the arrival array
 
     if (!fp.gemm_only) {
     // ------------------------------------------------------------------ phase 1: local histogram, publish counts
-    {
-        const int64_t* idx = reinterpret_cast<const int64_t*>(rp.sym + rp.sl.topk_idx);
-        const float* tw = reinterpret_cast<const float*>(rp.sym + rp.sl.topk_weights);
-        for (int i = tid; i < n_routes; i += nthr) {
-            const int64_t e64 = idx[i];
-            const bool ok = e64 >= 0 && e64 < rp.E && tw[i] != 0.0f;
-            rs.expert[i] = ok ? static_cast<short>(e64) : static_cast<short>(-1);
-            if (ok) atomicAdd(&rs.hist[static_cast<int>(e64)], 1);
+    // This CTA pushes the contiguous share [lo, hi) of the rank's routes; `before` counts, per expert, the valid routes
+    // in front of the share, so the CTA can number its routes without talking to the other CTAs.
+    const int per_cta = (n_routes + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
+    const int lo = min(static_cast<int>(blockIdx.x) * per_cta, n_routes), hi = min(lo + per_cta, n_routes);
+    const int64_t* idx = reinterpret_cast<const int64_t*>(rp.sym + rp.sl.topk_idx);
+    const float* tw = reinterpret_cast<const float*>(rp.sym + rp.sl.topk_weights);
+    for (int i = tid; i < n_routes; i += nthr) {
+        const int64_t e64 = idx[i];
+        if (e64 >= 0 && e64 < rp.E && tw[i] != 0.0f) {
+            atomicAdd(&rs.hist[static_cast<int>(e64)], 1);
+            if (i < lo) atomicAdd(&rs.before[static_cast<int>(e64)], 1);
         }
     }
     __syncthreads();
@@ -183,7 +337,7 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
     }
 
     // ------------------------------------------------------------------ phase 2: all ranks' counts, plan
-    if (tid < rp.R) {
+    if (tid < rp.R && s_misc[1]) {
         int seen = 0;
         const int* sig = reinterpret_cast<const int*>(rp.sym + rp.sl.signals) + MM_BAR_COUNTS * MM_MAX_RANKS + tid;
         if (!wait_flag_ge(sig, epoch, true, status, rp.barrier_timeout_ns, &seen)) {
@@ -222,9 +376,8 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
                 run = 0;
             }
             s_misc[0] = run / MM_BLOCK_M;
-            int* plan = reinterpret_cast<int*>(rp.scratch + rp.cl.plan);
-            plan[0] = run / MM_BLOCK_M;   // every CTA writes the same values
-            plan[1] = run;
+            fp.plan[MM_PLAN_MBLOCKS] = run / MM_BLOCK_M;   // every CTA writes the same values
+            fp.plan[MM_PLAN_ROWS_PADDED] = run;
         }
     }
     __syncthreads();
@@ -253,46 +406,47 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
             }
         }
     }
-    } else if (tid == 0) {
-        s_misc[0] = fp.g1.plan[0];      // the plan was made by route_plan_kernel
-    }
     __threadfence();
     __syncthreads();
     if (tid == 0) stamp(5);
-    const int num_mblocks = s_misc[0];
-    const bool healthy = s_misc[1] != 0;
-    const int rows_expected = s_misc[2];
-    const int arrive_total_slot = static_cast<int>(rp.sl.pool_rows / MM_BLOCK_M);   // last word of the arrival array
 
     // ------------------------------------------------------------------ phase 3: push this CTA's share of the rows
-    if (healthy && !fp.gemm_only) {
+    if (s_misc[1]) {
+        int* dest_row = reinterpret_cast<int*>(rp.scratch + rp.cl.dest_row);
+        // 3a. one warp numbers the share's routes in route order: a route's pool row on the owner is the expert's base for
+        //     this rank + the rank's earlier routes to that expert (those before the share, then those inside it).
+        if (warp == 0) {
+            for (int i0 = lo; i0 < hi; i0 += 32) {
+                const int i = i0 + lane;
+                int e = -1;
+                if (i < hi) {
+                    const int64_t e64 = idx[i];
+                    if (e64 >= 0 && e64 < rp.E && tw[i] != 0.0f) e = static_cast<int>(e64);
+                }
+                const unsigned same = __match_any_sync(0xffffffffu, e);
+                const int ahead = __popc(same & ((1u << lane) - 1u));
+                int row = -1;
+                if (e >= 0) row = rs.dest[e] + rs.before[e] + ahead;
+                __syncwarp();
+                if (e >= 0 && ahead == 0) rs.before[e] += __popc(same);
+                __syncwarp();
+                if (row >= rp.sl.pool_rows) row = -1;          // cannot happen with worst-case sizing; never write out of bounds
+                if (i < hi) dest_row[i] = row;
+            }
+        }
+        __syncthreads();
+        // 3b. all warps copy rows (H bytes of fp8 + 16 bytes of metadata each) into the owners' pools
         const uint8_t* x = rp.sym + rp.sl.x;
         const float* x_sf = reinterpret_cast<const float*>(rp.sym + rp.sl.x_sf);
-        const float* tw = reinterpret_cast<const float*>(rp.sym + rp.sl.topk_weights);
-        int* dest_row = reinterpret_cast<int*>(rp.scratch + rp.cl.dest_row);
         const int warps_per_cta = nthr >> 5;
-        for (int i = blockIdx.x * warps_per_cta + warp; i < n_routes; i += gridDim.x * warps_per_cta) {
-            const int e = rs.expert[i];
-            if (e < 0) { if (lane == 0) dest_row[i] = -1; continue; }
-            // slot inside the expert: routes of this rank are ordered by (token, top-k slot) == route index
-            int within = 0;
-            for (int j = lane; j < i; j += 32) within += (rs.expert[j] == e);
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) within += __shfl_xor_sync(0xffffffffu, within, o);
-            const int row = rs.dest[e] + within;
-            if (lane == 0) dest_row[i] = row;
+        for (int i = lo + warp; i < hi; i += warps_per_cta) {
+            const int row = dest_row[i];
+            if (row < 0) continue;
+            const int e = static_cast<int>(idx[i]);
             const int token = i / rp.K, slot = i - token * rp.K;
             uint8_t* peer = reinterpret_cast<uint8_t*>(rp.peers[e / rp.E_loc]);
-            const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<int64_t>(token) * rp.H);
-            uint4* dst = reinterpret_cast<uint4*>(peer + rp.sl.pool_x + static_cast<int64_t>(row) * rp.H);
-            const int nvec = rp.H / 16;
-            for (int v0 = 0; v0 < nvec; v0 += 32 * 8) {
-                uint4 buf[8];
-#pragma unroll
-                for (int k = 0; k < 8; ++k) { const int v = v0 + k * 32 + lane; if (v < nvec) buf[k] = __ldg(src + v); }
-#pragma unroll
-                for (int k = 0; k < 8; ++k) { const int v = v0 + k * 32 + lane; if (v < nvec) dst[v] = buf[k]; }
-            }
+            push_two_rows(x + static_cast<int64_t>(token) * rp.H, peer + rp.sl.pool_x + static_cast<int64_t>(row) * rp.H, nullptr, nullptr,
+                          rp.H, lane);
             if (lane == 0) {
                 MmPoolMeta m;
                 m.x_scale = x_sf[token];
@@ -307,12 +461,12 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
         // barrier), then the arrival counters of all its rows, one row per lane, as relaxed reductions.
         __syncwarp();
         __threadfence_system();
-        for (int i0 = blockIdx.x * warps_per_cta + warp; i0 < n_routes; i0 += 32 * gridDim.x * warps_per_cta) {
-            const int i = i0 + lane * gridDim.x * warps_per_cta;
-            if (i < n_routes) {
-                const int e = rs.expert[i];
-                if (e >= 0) {
-                    const int row = __ldcg(dest_row + i);     // written by lane 0 above, before the fence
+        for (int i0 = lo + warp; i0 < hi; i0 += 32 * warps_per_cta) {
+            const int i = i0 + lane * warps_per_cta;
+            if (i < hi) {
+                const int row = dest_row[i];
+                if (row >= 0) {
+                    const int e = static_cast<int>(idx[i]);
                     int* arr = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(rp.peers[e / rp.E_loc]) + rp.sl.pool_arrive);
                     asm volatile("red.relaxed.sys.global.add.s32 [%0], 1;" ::"l"(arr + row / MM_BLOCK_M) : "memory");
                     asm volatile("red.relaxed.sys.global.add.s32 [%0], 1;" ::"l"(arr + arrive_total_slot) : "memory");
@@ -320,103 +474,40 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
             }
         }
     }
+    } else if (tid == 0) {
+        s_misc[0] = s_misc[1] ? fp.plan[MM_PLAN_MBLOCKS] : 0;      // the plan was made by route_plan_kernel
+        s_misc[2] = fp.plan[MM_PLAN_ROWS_EXPECTED];
+    }
     // the routing scratch is dead from here on; the operand ring (same shared memory) is written by TMA next
     fence_proxy_async_smem();
     __syncthreads();
     if (tid == 0) stamp(6);
+    const int num_mblocks = s_misc[0];
+    const bool healthy = s_misc[1] != 0;
+    const int rows_expected = s_misc[2];
 
-    // ------------------------------------------------------------------ phase 4: GEMM1 tiles, then GEMM2 tiles
+    // ------------------------------------------------------------------ phase 4: the tile loop
     const GemmParams& g1 = fp.g1;
     const GemmParams& g2 = fp.g2;
-    // Tile order: m-blocks are grouped in waves of `wave_mblocks`; with G1(k) / G2(k) = all GEMM1 / GEMM2 tiles of wave k
-    // and R(k) = one requantisation tile per m-block of wave k (epilogue warps only), the global order is
-    //     G1(0), G1(1), [R(0), G1(2), G2(0)], [R(1), G1(3), G2(1)], ..., [R(n-1), G2(n-1)]
-    // Interleaving the two GEMMs spreads the combine stores (NVLink) over the whole compute phase; R(k) comes a full
-    // wave after G1(k) and G2(k) a full wave after R(k), so their waits are normally satisfied on arrival.
-    // Every wait is for tiles that come earlier in this order and every role of a CTA walks its tiles in order, so the
-    // waits cannot form a cycle.
     const int nb1 = g1.n_blocks, nb2 = g2.n_blocks;
     const WaveOrder order_init(num_mblocks, max(1, fp.wave_mblocks), nb1, nb2);
-    const int tiles_all = healthy ? num_mblocks * (nb1 + 1 + nb2) : 0;
+    const int tiles_all = healthy ? num_mblocks * (nb1 + nb2) : 0;
+    const int requant_units = healthy ? num_mblocks * 4 : 0;
     const int* arrive = reinterpret_cast<const int*>(rp.sym + rp.sl.pool_arrive);
-
-    // Requantisation tile, run by all eight epilogue warps: wait until every GEMM1 tile of the m-block is stored (each
-    // epilogue warp of each of its n_blocks tiles counts once), turn its bf16 rows into e4m3 with one scale per row, two
-    // rows per warp at a time, and release the m-block to GEMM2.
-    auto requantise_mblock = [&](int mb) -> bool {
-        const int valid = g1.mblock_valid[mb];
-        if (warp == 2 && lane == 0) {
-            int seen = 0;
-            const int target = nb1 * kEpilogueWarps;
-            const bool ok = wait_flag_ge(fp.l1_done + mb, target, false, status, g1.timeout_ns, &seen);
-            if (!ok) {
-                report_status(rp.scratch, rp.cl, MM_ERR_GRID_BARRIER_TIMEOUT, 4, mb, target, seen);
-                *abort_flag = 1;
-            }
-            s_misc[3] = ok ? 1 : 0;
-        }
-        named_bar_sync(2, kEpilogueThreads);
-        const bool ok = s_misc[3] != 0;
-        if (ok) {
-            __threadfence();
-            const int inter = g1.n_out, vecs = inter / 8;
-            const int ew = warp - 2;
-            for (int r = ew; r < valid; r += 2 * kEpilogueWarps) {
-                uint4 buf[2][8];
-                float inv[2], sc2[2];
-#pragma unroll
-                for (int u = 0; u < 2; ++u) {
-                    const int64_t prow = static_cast<int64_t>(mb) * kBlockM + min(r + u * kEpilogueWarps, valid - 1);
-                    const float amax = __uint_as_float(__ldcg(g1.row_amax + prow));
-                    sc2[u] = fmaxf(__fdiv_rn(amax, 448.0f), 1.0e-4f);
-                    inv[u] = __fdiv_rn(1.0f, sc2[u]);
-                    const uint4* src = reinterpret_cast<const uint4*>(g1.act_bf16 + prow * inter);
-#pragma unroll
-                    for (int k = 0; k < 8; ++k) { const int v = k * 32 + lane; if (v < vecs) buf[u][k] = __ldcg(src + v); }
-                }
-#pragma unroll
-                for (int u = 0; u < 2; ++u) {
-                    if (r + u * kEpilogueWarps >= valid) continue;
-                    const int64_t prow = static_cast<int64_t>(mb) * kBlockM + r + u * kEpilogueWarps;
-                    const uint4* src = reinterpret_cast<const uint4*>(g1.act_bf16 + prow * inter);
-                    uint2* dst = reinterpret_cast<uint2*>(fp.act_fp8 + prow * inter);
-                    for (int v0 = 0; v0 < vecs; v0 += 32 * 8) {
-#pragma unroll
-                        for (int k = 0; k < 8; ++k) {
-                            const int v = v0 + k * 32 + lane;
-                            if (v < vecs) {
-                                const uint4 d = (v0 == 0) ? buf[u][k] : __ldcg(src + v);
-                                uint2 o;
-                                o.x = pack4_e4m3(bf16_lo(d.x) * inv[u], bf16_hi(d.x) * inv[u], bf16_lo(d.y) * inv[u], bf16_hi(d.y) * inv[u]);
-                                o.y = pack4_e4m3(bf16_lo(d.z) * inv[u], bf16_hi(d.z) * inv[u], bf16_lo(d.w) * inv[u], bf16_hi(d.w) * inv[u]);
-                                dst[v] = o;
-                            }
-                        }
-                    }
-                    if (lane == 0) { fp.act_scale_w[prow] = sc2[u]; g1.row_amax[prow] = 0u; }
-                }
-            }
-        }
-        named_bar_sync(2, kEpilogueThreads);             // all rows of the m-block are requantised
-        if (ok && warp == 2 && lane == 0) {
-            __threadfence();
-            atomicAdd(fp.l2_ready + mb, 4);              // GEMM2 producers wait for 4
-            atomicAdd(fp.grid_sync + 2, 1);
-        }
-        return ok;
-    };
 
     if (warp == 0) {
         // -------------------------------------------------------------- TMA producer
         int stage = 0; uint32_t phase = 0;
         bool alive = true;
         // once every row has arrived (every m-block is requantised) no further per-tile polling is needed
-        bool all_arrived = fp.gemm_only != 0, all_ready = false;
+        bool all_arrived = false, all_ready = false;
         WaveOrder order = order_init;
+        int local_i = -1;                                   // index of the tile in this CTA's sequence
+        uint64_t polled_g1 = 0, polled_g2 = 0;              // time this warp itself spent polling for GEMM1 / GEMM2 tiles (tuning aid)
         for (int tile = blockIdx.x; tile < tiles_all && alive; tile += gridDim.x) {
             int kind, mb, nb;
             order.seek(tile, kind, mb, nb);
-            if (kind == WaveOrder::kRequant) continue;          // epilogue warps only
+            ++local_i;
             const bool second = kind == WaveOrder::kG2;
             const GemmParams& g = second ? g2 : g1;
             const int e = g.mblock_expert[mb];
@@ -431,24 +522,33 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
                     mbar_arrive_expect_tx(full_bar(stage), kStageBytes);
                     tma_load_2d(a_dst + kABytes, tb, 0, (b_tile0 + kb) * kBlockN, full_bar(stage));   // weights first
                 }
-                if (kb == 0 && !(second ? all_ready : all_arrived)) {
-                    // the token operand of this m-block must be complete before TMA may read it
+                // The token operand of this m-block must be complete before TMA may read it.  Normally the scout (an epilogue
+                // lane that polls ahead while it waits for accumulators) has confirmed that already, and this warp, whose
+                // loads the tensor pipe is waiting for, only reads a shared-memory word; otherwise it polls itself.
+                if (kb == 0 && local_i >= *reinterpret_cast<volatile int*>(s_misc + 4) && !(second ? all_ready : all_arrived)) {
                     int seen = 0;
                     bool ok = true;
+                    const uint64_t t_poll = global_timer_ns();
                     if (second) {
-                        all_ready = ld_acquire_gpu(fp.grid_sync + 2) - num_mblocks >= 0;
+                        all_ready = ld_acquire_gpu(fp.grid_sync + 2) - requant_units >= 0;
                         if (!all_ready) ok = wait_flag_ge(fp.l2_ready + mb, 4, false, status, g.timeout_ns, &seen);
                     } else {
                         all_arrived = ld_acquire_sys(arrive + arrive_total_slot) - rows_expected >= 0;
                         if (!all_arrived) ok = wait_flag_ge(arrive + mb, g.mblock_valid[mb], true, status, rp.barrier_timeout_ns, &seen);
                     }
+                    if (second) polled_g2 += global_timer_ns() - t_poll; else polled_g1 += global_timer_ns() - t_poll;
                     if (!ok) {
                         if (lane == 0) report_status(rp.scratch, rp.cl, MM_ERR_GRID_BARRIER_TIMEOUT, second ? 2 : 1, mb,
                                                      second ? 4 : g.mblock_valid[mb], seen);
                         *abort_flag = 1;
                         alive = false;
                     }
-                    // rows were written with ordinary stores (by other SMs or GPUs); order them before the TMA reads
+                }
+                if (kb == 0) {
+                    // rows were written with ordinary stores (by other SMs or GPUs) and their completion was observed with an
+                    // acquire load (here, or by the scout, whose result came through shared memory): order all that before
+                    // the TMA reads
+                    __threadfence_block();
                     asm volatile("fence.proxy.async;" ::: "memory");
                 }
                 // issue the token tile even on failure so that the stage's byte count completes and nobody is left waiting
@@ -458,7 +558,10 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
                 if (!alive) break;
             }
         }
-        if (lane == 0) stamp(7);
+        if (lane == 0) {
+            stamp(7);
+            if (blockIdx.x == 0) { status[14] = static_cast<int>(polled_g1 / 100); status[15] = static_cast<int>(polled_g2 / 100); }
+        }
     } else if (warp == 1) {
         // -------------------------------------------------------------- MMA issuer
         constexpr uint32_t idesc = umma_idesc_f8(kBlockM, kBlockN);
@@ -469,7 +572,6 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
         for (int tile = blockIdx.x; tile < tiles_all && alive; tile += gridDim.x) {
             int kind, mb, nb;
             order.seek(tile, kind, mb, nb);
-            if (kind == WaveOrder::kRequant) continue;
             const GemmParams& g = kind == WaveOrder::kG2 ? g2 : g1;
             const int k_blocks = g.kdim / kBlockK;
             if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, g.timeout_ns)) { alive = false; break; }
@@ -493,24 +595,106 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
             if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
         }
         if (lane == 0) stamp(8);
+    } else if (warp < kFusedFirstEpilogueWarp) {
+        // -------------------------------------------------------------- helpers
+        // Two jobs:
+        // (a) gemm_only: push this rank's rows in send-list order.  Chunks of the list are claimed with an atomic counter, so
+        //     the helper warps of the whole grid walk it front to back together.  After a chunk's rows are written: warp
+        //     barrier, one system-scope fence, then one arrival per row on the owner (per m-block and in total).
+        // (b) requantisation units, claimed in m-block order by the helper warps of all CTAs: once every GEMM1 tile of the
+        //     m-block is stored (each of the 8 epilogue warps of each of its nb1 tiles counts once), turn 32 of its bf16 rows
+        //     into e4m3 with one scale per row (deep_gemm/include/deep_gemm/impls/mega_moe_dcu_tiles.cuh:672-733) and count
+        //     the quarter towards l2_ready[m-block].
+        // Both loops are kept as simple as this on purpose: merged into one loop the compiler spills the row buffers and the
+        // helper warps fall behind the tile loop (measured).
+        const int n_send = (fp.gemm_only && healthy) ? fp.plan[MM_PLAN_SEND] : 0;
+        const int l1_target = nb1 * kEpilogueWarps;
+
+        int* requant_head = fp.grid_sync + MM_SYNC_REQUANT_HEAD;
+        // (a) push: walk the send list until it is exhausted (policy bit 0 clear: only warp 2 of a CTA pushes once several
+        //     ranks are involved, so that warp 3 requantises from the start and GEMM2 tiles never wait for the link)
+        const bool pusher = (fp.policy & 1) != 0 || rp.R == 1 || warp == 2;
+        while (pusher) {
+            int j0 = 0;
+            if (lane == 0) j0 = atomicAdd(fp.grid_sync + MM_SYNC_PUSH_HEAD, kPushChunk);
+            j0 = __shfl_sync(0xffffffffu, j0, 0);
+            if (j0 >= n_send) break;
+            push_chunk(fp, j0, n_send, lane);
+        }
+        if (warp == 2 && lane == 0) stamp(12);
+        // (b) requantisation: claim the units in order and wait for each
+        while (true) {
+            int u = 0;
+            if (lane == 0) u = atomicAdd(requant_head, 1);
+            u = __shfl_sync(0xffffffffu, u, 0);
+            if (u >= requant_units) break;
+            int ok = 1;
+            if (lane == 0) {
+                int seen = 0;
+                if (!wait_flag_ge(fp.l1_done + (u >> 2), l1_target, false, status, g1.timeout_ns, &seen, 200)) {
+                    report_status(rp.scratch, rp.cl, MM_ERR_GRID_BARRIER_TIMEOUT, 4, u >> 2, l1_target, seen);
+                    ok = 0;
+                }
+            }
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) break;
+            requant_unit(fp, u, lane);
+        }
+        if (warp == 2 && lane == 0) stamp(13);
     } else {
-        // -------------------------------------------------------------- epilogue (warps 2..9)
-        const int q = warp & 3;
-        const int half = (warp - 2) >> 2;
+        // -------------------------------------------------------------- epilogue (eight warps)
+        const int ew = warp - kFusedFirstEpilogueWarp;
+        const int q = warp & 3;                       // TMEM lane quarter this warp may read
+        const int half = ew >> 2;                     // which half of the tile's output columns
         const int et = q * 32 + lane;
-        uint8_t* my_staging = staging_gen + (warp - 2) * kStagingWarpBytes;
+        uint8_t* my_staging = staging_gen + ew * kStagingWarpBytes;
         const bool do_clamp = g1.clamp < 3.0e38f;
         int acc = 0; uint32_t acc_phase = 0;
         bool alive = true;
         WaveOrder order = order_init;
+        // Until this CTA's first accumulator is complete the epilogue warps have nothing to do: they help the helper warps
+        // push rows (gemm_only), which gets most of a single GPU's rows into the pool within the first tile's time.
+        if (fp.gemm_only && healthy && (fp.policy & 2)) {
+            const int n_send = fp.plan[MM_PLAN_SEND];
+            while (true) {
+                int j0 = n_send;
+                if (lane == 0 && !mbar_try_wait(tfull_bar(0), 0)) j0 = atomicAdd(fp.grid_sync + MM_SYNC_PUSH_HEAD, kPushChunk);
+                j0 = __shfl_sync(0xffffffffu, j0, 0);
+                if (j0 >= n_send) break;
+                push_chunk(fp, j0, n_send, lane);
+            }
+        }
+        // Scout: one lane checks, without blocking, whether the dependencies of this CTA's NEXT tiles are met (arrival
+        // counter of a GEMM1 tile's m-block, requantisation count of a GEMM2 tile's) and publishes how many leading tiles
+        // are confirmed.  It polls while the epilogue waits for an accumulator, so the producer warp does not have to put a
+        // global-memory round trip in front of every tile.  Counters only grow during a call: a confirmation stays valid.
+        const bool is_scout = warp == kFusedFirstEpilogueWarp && lane == 0;
+        WaveOrder scout_order = order_init;
+        int scout_tile = blockIdx.x, scout_n = 0, scout_polls = 0;
+        bool scout_all_arrived = false, scout_all_ready = false;
+        auto scout_step = [&]() {
+            for (int n = 0; n < 2 && scout_tile < tiles_all; ++n) {
+                int kind, mb, nb;
+                scout_order.seek(scout_tile, kind, mb, nb);
+                bool ok;
+                if (kind == WaveOrder::kG2) {
+                    if (!scout_all_ready && (scout_polls++ & 7) == 0) scout_all_ready = ld_acquire_gpu(fp.grid_sync + 2) - requant_units >= 0;
+                    ok = scout_all_ready || ld_acquire_gpu(fp.l2_ready + mb) - 4 >= 0;
+                } else {
+                    if (!scout_all_arrived && (scout_polls++ & 7) == 0) scout_all_arrived = ld_acquire_sys(arrive + arrive_total_slot) - rows_expected >= 0;
+                    ok = scout_all_arrived || ld_acquire_sys(arrive + mb) - g1.mblock_valid[mb] >= 0;
+                }
+                if (!ok) break;
+                scout_tile += gridDim.x;
+                ++scout_n;
+            }
+            __threadfence_block();
+            *reinterpret_cast<volatile int*>(s_misc + 4) = scout_n;
+        };
         for (int tile = blockIdx.x; tile < tiles_all && alive; tile += gridDim.x) {
             if (*abort_flag != 0) break;
             int kind, mb, nb;
             order.seek(tile, kind, mb, nb);
-            if (kind == WaveOrder::kRequant) {
-                if (!requantise_mblock(mb)) { alive = false; break; }
-                continue;
-            }
             const bool second = kind == WaveOrder::kG2;
             const GemmParams& g = second ? g2 : g1;
             const int e = g.mblock_expert[mb];
@@ -519,7 +703,7 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
             const bool row_ok = et < valid;
             float* sc = scales_gen + acc * kBlockN;
             {
-                const int st = (warp - 2) * 32 + lane;
+                const int st = ew * 32 + lane;
                 const float* ws = g.w_scale + static_cast<int64_t>(e) * g.w_rows_per_expert;
                 if (!second) {
                     sc[st] = st < 128 ? ws[nb * 128 + st] : ws[g.w_rows_per_expert / 2 + nb * 128 + (st - 128)];
@@ -529,6 +713,8 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
                 }
             }
             named_bar_sync(1, kEpilogueThreads);
+            if (is_scout) scout_step();
+            __syncwarp();
             if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, g.timeout_ns)) { alive = false; break; }
             tc_fence_after();
             // the accumulator is complete, so the m-block's rows (and, for GEMM2, its activation scales) are in place
@@ -541,10 +727,7 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
                     route_w = __uint_as_float(raw.y);
                 } else {
                     row_scale = __ldcg(g.act_scale + row);
-                    const int src_info = static_cast<int>(raw.w);
-                    const int src_rank = src_info >> 8, slot = src_info & 0xff;
-                    out_ptr = reinterpret_cast<uint8_t*>(g.peers[src_rank]) + g.combine_off +
-                              (static_cast<int64_t>(slot) * g.T + static_cast<int>(raw.z)) * g.H * 2;
+                    out_ptr = combine_row_ptr(g, static_cast<int>(raw.w), static_cast<int>(raw.z));
                 }
             }
             if (!second) epilogue_math<0>(g1, tmem_base, sc, my_staging, lane, q, half, acc, mb, nb, valid, row, row_ok, row_scale, route_w, out_ptr, do_clamp);
@@ -581,7 +764,8 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
             __threadfence_system();
         }
         __syncthreads();
-        if (tid < rp.R) {
+        // after a failure this rank stays silent: its peers' own bounded waits expire and each records a status
+        if (tid < rp.R && ld_acquire_gpu(status) == 0) {
             int* sig = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(rp.peers[tid]) + rp.sl.signals);
             st_release_sys(sig + MM_BAR_COMBINE * MM_MAX_RANKS + rp.rank, epoch);
         }
@@ -596,7 +780,7 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
     if (tid == 0) stamp(10);
 
     // ------------------------------------------------------------------ phase 6: top-k reduce in slot order
-    {
+    if (ld_acquire_gpu(status) == 0) {      // after a failure y stays untouched
         const int vecs = rp.H / 8;
         const int64_t total = static_cast<int64_t>(n_tokens) * vecs;
         const int64_t* topk_idx = reinterpret_cast<const int64_t*>(rp.sym + rp.sl.topk_idx);
@@ -637,11 +821,12 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
     if (tid == 0) stamp(11);
     {
         int* arr = reinterpret_cast<int*>(rp.sym + rp.sl.pool_arrive);
-        for (int i = blockIdx.x * nthr + tid; i < num_mblocks; i += gridDim.x * nthr) { arr[i] = 0; fp.l2_ready[i] = 0; }
-        for (int i = blockIdx.x * nthr + tid; i < num_mblocks * 4; i += gridDim.x * nthr) fp.l1_done[i] = 0;
+        for (int i = blockIdx.x * nthr + tid; i < num_mblocks; i += gridDim.x * nthr) { arr[i] = 0; fp.l2_ready[i] = 0; fp.l1_done[i] = 0; }
         if (blockIdx.x == 0 && tid == 0) {
             arr[arrive_total_slot] = 0;
             fp.grid_sync[2] = 0;
+            fp.grid_sync[MM_SYNC_REQUANT_HEAD] = 0;
+            fp.grid_sync[MM_SYNC_PUSH_HEAD] = 0;
             reinterpret_cast<int*>(rp.scratch + rp.cl.epoch)[0] = epoch;
             fp.grid_sync[1] = fused_calls + 1;
         }

@@ -56,10 +56,21 @@ struct GemmParams {
     uint64_t peers[MM_MAX_RANKS];
     int64_t combine_off;
     int T, H;
+    int R, K;                  // ranks and top-k slots: bounds of the (source rank, slot) a pool row may name
     // error reporting
     int* status;               // MmStatus*
     uint64_t timeout_ns;
 };
+
+// Destination of one GEMM2 output row: combine[slot][token][:] on the SOURCE rank.  The row's metadata was written by
+// that rank; a pool row nobody wrote in this call (error path, stale or uninitialised memory) may name anything, so the
+// three indices are range-checked and a row that fails the check is not stored at all.
+__device__ __forceinline__ uint8_t* combine_row_ptr(const GemmParams& p, int src_info, int src_token) {
+    const int src_rank = src_info >> 8, slot = src_info & 0xff;
+    if (src_rank < 0 || src_rank >= p.R || slot >= p.K || src_token < 0 || src_token >= p.T) return nullptr;
+    return reinterpret_cast<uint8_t*>(p.peers[src_rank]) + p.combine_off +
+           (static_cast<int64_t>(slot) * p.T + src_token) * p.H * 2;
+}
 
 // x * sigmoid(x) with the fast exponential and reciprocal units, as the reference does
 // (deep_gemm/include/deep_gemm/common/mega_moe_dcu.cuh:90-99: exp2 and rcp intrinsics)
@@ -195,7 +206,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    const int num_mblocks = p.plan[0];
+    // after a failed bounded wait earlier in the call (status code set) the plan is not trustworthy: run no tile
+    const int num_mblocks = p.status[0] != 0 ? 0 : p.plan[0];
     const int num_tiles = num_mblocks * p.n_blocks;
     const int k_blocks = p.kdim / kBlockK;
 
@@ -301,9 +313,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                 } else {
                     const MmPoolMeta m = p.meta[row];
                     row_scale = p.act_scale[row];
-                    const int src_rank = m.src_info >> 8, slot = m.src_info & 0xff;
-                    out_ptr = reinterpret_cast<uint8_t*>(p.peers[src_rank]) + p.combine_off +
-                              (static_cast<int64_t>(slot) * p.T + m.src_token) * p.H * 2;
+                    out_ptr = combine_row_ptr(p, m.src_info, m.src_token);
                 }
             }
             if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.timeout_ns)) { alive = false; break; }

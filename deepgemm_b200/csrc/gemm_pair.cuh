@@ -93,7 +93,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    const int num_pairs = p.plan[2];
+    const int num_pairs = p.status[0] != 0 ? 0 : p.plan[2];   // no tile after a failed bounded wait earlier in the call
     const int num_tiles = num_pairs * p.n_blocks;
     const int k_blocks = p.kdim / kBlockK;
     const int first_tile = blockIdx.x >> 1, tile_step = gridDim.x >> 1;
@@ -195,9 +195,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
                     route_w = m.route_weight;
                 } else {
                     row_scale = p.act_scale[row];
-                    const int src_rank = m.src_info >> 8, slot = m.src_info & 0xff;
-                    out_ptr = reinterpret_cast<uint8_t*>(p.peers[src_rank]) + p.combine_off +
-                              (static_cast<int64_t>(slot) * p.T + m.src_token) * p.H * 2;
+                    out_ptr = combine_row_ptr(p, m.src_info, m.src_token);
                 }
             }
             if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.timeout_ns)) { alive = false; break; }

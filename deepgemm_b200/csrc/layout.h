@@ -62,17 +62,22 @@ struct MmSymLayout {
 struct MmScratchLayout {
     int64_t status;        // MmStatus
     int64_t epoch;         // int32 [4]: [0] call epoch used by the cross-rank barriers, [1..] grid-barrier words
-    int64_t plan;          // int32 [8]: [0] num_mblocks, [1] pool rows in use
+    int64_t plan;          // int32 [8]: [0] num_mblocks, [1] pool rows in use (padded), [2] m-block pairs, [3] valid routes of this
+                           //            rank (length of send_list), [6] rows to receive
     int64_t block_counts;  // int32 [route_blocks][E]   per-block histogram, then exclusive prefix over blocks
     int64_t dest_base;     // int32 [E]   first pool row (on the owner) for this rank's routes to expert e
     int64_t expert_total;  // int32 [E_loc]
     int64_t expert_off;    // int32 [E_loc]
     int64_t mblock_expert; // int32 [pool_rows / MM_BLOCK_M]
     int64_t mblock_valid;  // int32 [pool_rows / MM_BLOCK_M]
-    int64_t l1_done;       // int32 [4 * pool_rows / MM_BLOCK_M]  GEMM1 tiles finished per (m-block, 32-row quarter) (fused)
-    int64_t l2_ready;      // int32 [pool_rows / MM_BLOCK_M]      quarters of an m-block requantised (fused)
-    int64_t grid_sync;     // int32 [4]  [0] CTA arrivals (monotonic), [1] fused calls completed, [2] m-blocks requantised
+    int64_t l1_done;       // int32 [pool_rows / MM_BLOCK_M]      epilogue-warp shares of GEMM1 tiles stored per m-block (layer kernel)
+    int64_t l2_ready;      // int32 [pool_rows / MM_BLOCK_M]      quarters of an m-block requantised (layer kernel)
+    int64_t grid_sync;     // int32 [8]  [0] CTA arrivals (monotonic), [1] fused calls completed, [2] requantisation units done,
+                           //            [3] push cursor into send_list, [4] requantisation-unit cursor
     int64_t dest_row;      // int32 [T][K]   pool row of each local route (-1 invalid); kept for inspection
+    int64_t send_base;     // int32 [E]      position in send_list of this rank's first route to expert e
+    int64_t send_list;     // int32x4 [T][K] this rank's valid routes in send order (local expert index, then owner rank):
+                           //                {route, pool row on the owner, owner rank, token}
     int64_t row_amax;      // u32   [pool_rows]  bit pattern of the non-negative row amax, self-resetting
     int64_t act_scale;     // f32   [pool_rows]
     int64_t act_bf16;      // bf16  [pool_rows][I]
@@ -125,10 +130,12 @@ static inline MmScratchLayout mm_scratch_layout_of(int R, int E, int T, int K, i
     L.expert_off = o;    o = mm_align(o + e_loc * 4, 256);
     L.mblock_expert = o; o = mm_align(o + pool_rows / MM_BLOCK_M * 4, 256);
     L.mblock_valid = o;  o = mm_align(o + pool_rows / MM_BLOCK_M * 4, 256);
-    L.l1_done = o;       o = mm_align(o + pool_rows / MM_BLOCK_M * 16, 256);
+    L.l1_done = o;       o = mm_align(o + pool_rows / MM_BLOCK_M * 4, 256);
     L.l2_ready = o;      o = mm_align(o + pool_rows / MM_BLOCK_M * 4, 256);
-    L.grid_sync = o;     o = mm_align(o + 16, 256);
+    L.grid_sync = o;     o = mm_align(o + 32, 256);
     L.dest_row = o;      o = mm_align(o + (int64_t)T * K * 4, 256);
+    L.send_base = o;     o = mm_align(o + (int64_t)E * 4, 256);
+    L.send_list = o;     o = mm_align(o + (int64_t)T * K * 16, 256);
     L.row_amax = o;      o = mm_align(o + pool_rows * 4, 256);
     L.act_scale = o;     o = mm_align(o + pool_rows * 4, 256);
     L.act_bf16 = o;      o = mm_align(o + pool_rows * I * 2, 1024);

@@ -62,10 +62,10 @@ __global__ void __launch_bounds__(256) quant_per_token_kernel(const __nv_bfloat1
 __global__ void __launch_bounds__(256) requant_kernel(const __nv_bfloat16* __restrict__ act, int inter,
                                                      const int* __restrict__ plan, const int* __restrict__ mblock_valid,
                                                      unsigned int* __restrict__ row_amax, float* __restrict__ act_scale,
-                                                     uint8_t* __restrict__ act_q) {
+                                                     uint8_t* __restrict__ act_q, const int* __restrict__ status) {
     __shared__ float s_inv[MM_BLOCK_M];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int num_mblocks = plan[0];
+    const int num_mblocks = status[0] != 0 ? 0 : plan[0];     // nothing to do after a failed bounded wait
     const int vecs = inter / 8;
     for (int mb = blockIdx.x; mb < num_mblocks; mb += gridDim.x) {
         const int valid = mblock_valid[mb];
@@ -123,9 +123,11 @@ __global__ void __launch_bounds__(256) requant_kernel(const __nv_bfloat16* __res
 // The reference zeroes those slots during its route scan; here they are skipped using the same validity rule.
 __global__ void __launch_bounds__(256, 4) combine_reduce_kernel(const uint8_t* __restrict__ sym, MmSymLayout sl, int E, int T, int K, int H,
                                                             int num_tokens, const int* __restrict__ runtime_num_tokens,
-                                                            __nv_bfloat16* __restrict__ y) {
+                                                            __nv_bfloat16* __restrict__ y, const int* __restrict__ status) {
+    if (status[0] != 0) return;       // a bounded wait expired earlier in the call: y stays untouched
+    // a device-side count (graph mode) never exceeds the launch-time count = rows of y
     int n = runtime_num_tokens ? *runtime_num_tokens : num_tokens;
-    n = min(max(n, 0), T);
+    n = min(max(n, 0), min(num_tokens, T));
     const int vecs = H / 8;
     const int64_t total = static_cast<int64_t>(n) * vecs;
     const int64_t* topk_idx = reinterpret_cast<const int64_t*>(sym + sl.topk_idx);

@@ -26,6 +26,7 @@ __device__ __align__(256) unsigned char g_static_work[MM_STATIC_WORK_BYTES];
 // use has to be asked for once per device, with that device current.
 std::mutex g_mu;
 void* g_work_ptr[64] = {nullptr};
+int64_t g_scratch_base[64] = {0};      // where the last call on each device put its scratch region (status words first)
 
 }  // namespace
 
@@ -83,6 +84,7 @@ int mm_fp8_w8a8_mega_moe_static(void* y, const void* x_fp8, const float* x_sf, c
             g_work_ptr[dev] = p;
         }
         work = static_cast<unsigned char*>(g_work_ptr[dev]);
+        g_scratch_base[dev] = scr_base;
     }
     unsigned char* sym = work;
     unsigned char* scr = work + scr_base;
@@ -105,6 +107,24 @@ int mm_fp8_w8a8_mega_moe_static(void* y, const void* x_fp8, const float* x_sf, c
     peers[0] = reinterpret_cast<uint64_t>(sym);
     return mm_fp8_w8a8_mega_moe(y, w1, s1, w2, s2, stats, sym, scr, peers, 0, 1, T, num_experts, num_tokens, K, H, I,
                                 activation_clamp, MM_MODE_STAGED, nullptr, stream_);
+}
+
+int mm_fp8_w8a8_mega_moe_static_status(void* stream_, int32_t* out5) {
+    if (!out5) return static_fail("mm_fp8_w8a8_mega_moe_static_status: null pointer");
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess || dev < 0 || dev >= 64) return static_fail("mm_fp8_w8a8_mega_moe_static_status: cudaGetDevice failed");
+    const unsigned char* status = nullptr;
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        if (!g_work_ptr[dev]) return static_fail("mm_fp8_w8a8_mega_moe_static_status: no static call has been made on this device");
+        status = static_cast<const unsigned char*>(g_work_ptr[dev]) + g_scratch_base[dev];
+    }
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    err = cudaMemcpyAsync(out5, status, 5 * sizeof(int32_t), cudaMemcpyDeviceToHost, stream);
+    if (err == cudaSuccess) err = cudaStreamSynchronize(stream);
+    if (err != cudaSuccess) return static_fail(cudaGetErrorString(err));
+    return 0;
 }
 
 }  // extern "C"

@@ -135,4 +135,21 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(128, 1) fp8_mma_peak
     if (warp == 0) { tc_fence_after(); tmem_dealloc_pair(tmem_base, 512); }
 }
 
+
+// Measurement aid: store `vecs` 16-byte vectors into each of `n_dst` destinations (device addresses; with peer-mapped
+// addresses this is the plain-store NVLink write rate the dispatch push and the GEMM2 combine stores can at best reach).
+// Every warp writes runs of 512 contiguous bytes, round-robin over the destinations, grid-stride.
+struct PeerStoreDsts { uint64_t ptr[MM_MAX_RANKS]; };
+__global__ void __launch_bounds__(256) peer_store_probe_kernel(PeerStoreDsts d, int n_dst, int64_t vecs) {
+    const uint4 v = make_uint4(threadIdx.x, blockIdx.x, 0x5a5a5a5au, 0xa5a5a5a5u);
+    const int64_t total = vecs * n_dst;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t run = i >> 5;                    // one 512-byte run per warp iteration
+        const int dst = static_cast<int>(run % n_dst);
+        const int64_t pos = (run / n_dst) * 32 + (i & 31);
+        if (pos < vecs) reinterpret_cast<uint4*>(d.ptr[dst])[pos] = v;
+    }
+}
+
 }  // namespace mm

@@ -26,9 +26,19 @@ struct RouteParams {
     uint64_t barrier_timeout_ns;
 };
 
+// Tokens of this call.  A device-side count (graph mode) is clamped to the launch-time count, which is the number of
+// rows of y the caller provided (deep_gemm/include/deep_gemm/impls/mega_moe_dcu.cuh:292 clamps the same way), so a
+// stale or oversized device value can never make a kernel write past the end of y.
 __device__ __forceinline__ int route_num_tokens(const RouteParams& p) {
-    int n = p.runtime_num_tokens ? *p.runtime_num_tokens : p.num_tokens;
-    return min(max(n, 0), p.T);
+    const int bound = min(p.num_tokens, p.T);
+    const int n = p.runtime_num_tokens ? *p.runtime_num_tokens : p.num_tokens;
+    return min(max(n, 0), bound);
+}
+
+// True once a bounded wait of this buffer has expired (or the pool overflowed): every later kernel of the call, and of
+// later calls until the buffers are re-initialised, returns at once instead of working on an unvalidated plan.
+__device__ __forceinline__ bool call_failed(const uint8_t* scratch, const MmScratchLayout& cl) {
+    return ld_acquire_gpu(reinterpret_cast<const int*>(scratch + cl.status)) != 0;
 }
 
 __device__ __forceinline__ void report_status(uint8_t* scratch, const MmScratchLayout& cl, int code, int phase, int rank,
@@ -142,10 +152,16 @@ __global__ void __launch_bounds__(1024) route_plan_kernel(RouteParams p) {
     __shared__ int tot[MM_MAX_EXPERTS];
     __shared__ int before[MM_MAX_EXPERTS];
     __shared__ int off[MM_MAX_EXPERTS];
-    if (p.R > 1) {
+    int* plan_w = reinterpret_cast<int*>(p.scratch + p.cl.plan);
+    bool ok = !call_failed(p.scratch, p.cl);
+    if (ok && p.R > 1) {
         const int epoch = reinterpret_cast<const int*>(p.scratch + p.cl.epoch)[0];
-        wait_rank_signals(p, MM_BAR_COUNTS, epoch);
-        __syncthreads();
+        ok = wait_rank_signals(p, MM_BAR_COUNTS, epoch);
+    }
+    if (!__syncthreads_and(ok)) {
+        // a rank's counts never arrived: leave an empty plan so that nothing downstream touches the pool or y
+        if (threadIdx.x == 0) { plan_w[0] = 0; plan_w[1] = 0; plan_w[2] = 0; plan_w[3] = 0; }
+        return;
     }
     const int* cm = reinterpret_cast<const int*>(p.sym + p.sl.count_matrix);
     for (int e = threadIdx.x; e < p.E; e += blockDim.x) {
@@ -170,15 +186,49 @@ __global__ void __launch_bounds__(1024) route_plan_kernel(RouteParams p) {
         }
         if (threadIdx.x == p.rank) {
             int* plan = reinterpret_cast<int*>(p.scratch + p.cl.plan);
+            int rows = 0;
+            for (int le = 0; le < p.E_loc; ++le) rows += tot[p.rank * p.E_loc + le];
             plan[0] = run / MM_BLOCK_M;
             plan[1] = run;
             plan[2] = pairs;
+            plan[6] = rows;                          // valid rows this rank receives
             if (run > p.sl.pool_rows) report_status(p.scratch, p.cl, MM_ERR_POOL_OVERFLOW, 0, p.rank, (int)p.sl.pool_rows, run);
         }
     }
     __syncthreads();
     int* dest_base = reinterpret_cast<int*>(p.scratch + p.cl.dest_base);
     for (int e = threadIdx.x; e < p.E; e += blockDim.x) dest_base[e] = off[e] + before[e];
+    // Send order of this rank's routes: by local expert index first, then by owner starting with the rank after this one
+    // (so that at any moment the ranks fill the same expert of every owner, and no two ranks start on the same owner).
+    // send_base[e] = exclusive prefix of this rank's own counts in that order.  E <= blockDim.x.
+    {
+        __shared__ int s_cnt[MM_MAX_EXPERTS];
+        __shared__ int s_warp[32];
+        auto order_of = [&](int e) { const int owner = e / p.E_loc, le = e - owner * p.E_loc; return le * p.R + (owner - p.rank - 1 + p.R) % p.R; };
+        for (int e = threadIdx.x; e < p.E; e += blockDim.x) s_cnt[order_of(e)] = cm[static_cast<int64_t>(p.rank) * p.E + e];
+        __syncthreads();
+        const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+        const int v = static_cast<int>(threadIdx.x) < p.E ? s_cnt[threadIdx.x] : 0;
+        int inc = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) { const int t = __shfl_up_sync(0xffffffffu, inc, o); if (lane >= o) inc += t; }
+        if (lane == 31) s_warp[wid] = inc;
+        __syncthreads();
+        if (wid == 0) {
+            int w = s_warp[lane];
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) { const int t = __shfl_up_sync(0xffffffffu, w, o); if (lane >= o) w += t; }
+            s_warp[lane] = w;                       // inclusive prefix of the warp totals
+        }
+        __syncthreads();
+        const int excl = inc - v + (wid > 0 ? s_warp[wid - 1] : 0);
+        __syncthreads();
+        if (static_cast<int>(threadIdx.x) < p.E) s_cnt[threadIdx.x] = excl;
+        __syncthreads();
+        int* send_base = reinterpret_cast<int*>(p.scratch + p.cl.send_base);
+        for (int e = threadIdx.x; e < p.E; e += blockDim.x) send_base[e] = s_cnt[order_of(e)];
+        if (threadIdx.x == 0) plan_w[3] = s_warp[31];     // valid routes of this rank == length of the send list
+    }
     int* e_tot = reinterpret_cast<int*>(p.scratch + p.cl.expert_total);
     int* e_off = reinterpret_cast<int*>(p.scratch + p.cl.expert_off);
     int* mb_e = reinterpret_cast<int*>(p.scratch + p.cl.mblock_expert);
@@ -204,6 +254,7 @@ constexpr int MM_DISPATCH_THREADS = 1024;
 __global__ void __launch_bounds__(MM_DISPATCH_THREADS) dispatch_kernel(RouteParams p) {
     __shared__ int s_e[MM_ROUTE_CHUNK];
     __shared__ int s_row[MM_ROUTE_CHUNK];
+    if (call_failed(p.scratch, p.cl)) return;
     const int n_routes = route_num_tokens(p) * p.K;
     const int route = blockIdx.x * MM_ROUTE_CHUNK + threadIdx.x;
     const bool owner_thread = threadIdx.x < MM_ROUTE_CHUNK;
@@ -270,9 +321,42 @@ __global__ void __launch_bounds__(MM_DISPATCH_THREADS) dispatch_kernel(RoutePara
     }
 }
 
+// ---- 4'. slot assignment + send list, no data movement (the layer kernel's helper warps push the rows) ------------
+// grid = route_blocks, block = MM_ROUTE_CHUNK.  Thread i owns route b*CHUNK+i.  Besides the pool row on the owner
+// (as in dispatch_kernel) it computes the route's position in this rank's send order and records
+// {route, row, owner rank, token} there, so a pushing warp needs one load per row to know what to copy where.
+__global__ void __launch_bounds__(MM_ROUTE_CHUNK) send_plan_kernel(RouteParams p) {
+    __shared__ int s_e[MM_ROUTE_CHUNK];
+    if (call_failed(p.scratch, p.cl)) return;
+    const int n_routes = route_num_tokens(p) * p.K;
+    const int route = blockIdx.x * MM_ROUTE_CHUNK + threadIdx.x;
+    int e = -1;
+    if (route < n_routes) {
+        const int64_t e64 = reinterpret_cast<const int64_t*>(p.sym + p.sl.topk_idx)[route];
+        const float w = reinterpret_cast<const float*>(p.sym + p.sl.topk_weights)[route];
+        if (e64 >= 0 && e64 < p.E && w != 0.0f) e = static_cast<int>(e64);
+    }
+    s_e[threadIdx.x] = e;
+    __syncthreads();
+    int row = -1;
+    if (e >= 0) {
+        int within = 0;
+        for (int j = 0; j < static_cast<int>(threadIdx.x); ++j) within += (s_e[j] == e);
+        const int earlier = reinterpret_cast<const int*>(p.scratch + p.cl.block_counts)[static_cast<int64_t>(blockIdx.x) * p.E + e] + within;
+        row = reinterpret_cast<const int*>(p.scratch + p.cl.dest_base)[e] + earlier;
+        if (row >= p.sl.pool_rows) row = -1;   // cannot happen with worst-case sizing; never write out of bounds
+        const int pos = reinterpret_cast<const int*>(p.scratch + p.cl.send_base)[e] + earlier;
+        if (pos >= 0 && pos < p.T * p.K)
+            reinterpret_cast<int4*>(p.scratch + p.cl.send_list)[pos] = make_int4(route, row, e / p.E_loc, route / p.K);
+    }
+    if (route < n_routes) reinterpret_cast<int*>(p.scratch + p.cl.dest_row)[route] = row;
+}
+
 // ---- cross-rank barrier as a kernel of its own (staged path) ---------------------------------------------------
 // grid = 1, block = 32: publish the call epoch on barrier `bar` of every rank, then wait for all ranks.
 __global__ void rank_barrier_kernel(RouteParams p, int bar) {
+    // after a failure this rank stays silent: its peers' own bounded waits expire and each of them records a status
+    if (call_failed(p.scratch, p.cl)) return;
     const int epoch = reinterpret_cast<const int*>(p.scratch + p.cl.epoch)[0];
     __threadfence_system();
     if (threadIdx.x < p.R) {

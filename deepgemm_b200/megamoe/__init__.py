@@ -38,10 +38,11 @@ _LARGE_OPT_DEFAULT_THRESHOLD = 256
 # un-prefixed aliases of the reference's environment variables
 _ALIASES = {_LARGE_OPT_ENV: "MEGAMOE_USE_STAGED", _LARGE_OPT_THRESHOLD_ENV: "MEGAMOE_STAGED_TOKEN_THRESHOLD"}
 
-# the fused single-launch variant is selected for token counts at or below the threshold; it keeps a rank's routes in
-# shared memory, so it is limited to this many routes (tokens x top-k) per rank -- larger calls always run staged
+# Kind of staged variant, snapshotted per buffer: by default the routing kernels are followed by ONE launch that pushes rows
+# over NVLink, runs GEMM1, requantises and runs GEMM2 with per-m-block dependencies; MEGAMOE_STAGED_SPLIT=1 selects separate
+# dispatch / barrier / GEMM1 / requantisation / GEMM2 launches instead.  All ranks of a group must use the same setting.
+_STAGED_SPLIT_ENV = "MEGAMOE_STAGED_SPLIT"
 _FUSED_AVAILABLE = True
-_FUSED_MAX_ROUTES = 4096
 
 
 def _align(value: int, alignment: int) -> int:
@@ -78,19 +79,14 @@ def _large_opt_3stage_selected(num_tokens: int, mode: str, threshold: int) -> bo
     return False
 
 
-def _eager_variant_is_staged(num_ranks: int, mode: str, threshold: int, y_tokens: int, dispatch_num_tokens: Optional[int],
-                             capacity: int, topk: int) -> bool:
-    """Variant of an eager (non-graph) call.  Every rank of a group must run the same variant (the staged launches and
-    the fused kernel signal one another differently), while ranks may hold different token counts
-    (tests/test_mega_moe_dcu.py:405-419 passes per-rank lists).  So with more than one rank the choice is made on what
-    all ranks share: the caller's dispatch_num_tokens if given, else the buffer's capacity per rank."""
+def _eager_variant_is_staged(mode: str, threshold: int, y_tokens: int, dispatch_num_tokens: Optional[int]) -> bool:
+    """Variant of an eager (non-graph) call, decided exactly as the reference does (megamoe/__init__.py:398-404): on
+    dispatch_num_tokens if given, else on y.size(0).  Every rank of a group must run the same variant (the staged launches
+    and the fused kernel signal one another differently), so when ranks hold different token counts the caller passes one
+    dispatch_num_tokens to all of them -- the reference's contract (README.md:165-177).  A mismatch does not deadlock here:
+    the bounded waits expire and SymmBuffer.check_status() reports it."""
     tokens = y_tokens if dispatch_num_tokens is None else int(dispatch_num_tokens)
-    if num_ranks > 1 and dispatch_num_tokens is None:
-        tokens = capacity
-    staged = _large_opt_3stage_selected(tokens, mode, threshold)
-    if not staged and mode != "off" and tokens * topk > _FUSED_MAX_ROUTES:
-        staged = True          # beyond the fused kernel's shared-memory routing capacity
-    return staged
+    return _large_opt_3stage_selected(tokens, mode, threshold)
 
 
 def _is_current_stream_capturing() -> bool:
@@ -276,6 +272,7 @@ class SymmBuffer:
         self.intermediate_hidden = int(intermediate_hidden)
         self._large_opt_3stage_mode = _large_opt_3stage_mode()
         self._large_opt_3stage_threshold = _large_opt_3stage_threshold()
+        self._staged_split = os.getenv(_STAGED_SPLIT_ENV, "0").strip().lower() in _LARGE_OPT_FORCE_VALUES
         self.cuda_graph_max_tokens_per_rank = int(cuda_graph_max_tokens_per_rank
                                                   if cuda_graph_max_tokens_per_rank is not None
                                                   else num_max_tokens_per_rank)
@@ -472,16 +469,10 @@ def fp8_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer: SymmBuffer
         dispatch_tokens = int(y.size(0)) if dispatch_num_tokens is None else int(dispatch_num_tokens)
         if dispatch_tokens < 0 or dispatch_tokens > int(sb.num_max_tokens_per_rank):
             raise ValueError(f"dispatch_num_tokens must be in 0..{int(sb.num_max_tokens_per_rank)}")
-        staged = _eager_variant_is_staged(sb.num_ranks, sb._large_opt_3stage_mode, sb._large_opt_3stage_threshold,
-                                          int(y.size(0)), dispatch_num_tokens, int(sb.num_max_tokens_per_rank), sb.num_topk)
+        staged = _eager_variant_is_staged(sb._large_opt_3stage_mode, sb._large_opt_3stage_threshold, int(y.size(0)),
+                                          dispatch_num_tokens)
         call_y = y
         runtime_ptr = None
-    if not staged and not graph_mode and int(call_y.size(0)) * sb.num_topk > _FUSED_MAX_ROUTES:
-        if sb.num_ranks > 1:
-            raise RuntimeError(f"the fused variant holds at most {_FUSED_MAX_ROUTES} routes (tokens x top-k) per rank; "
-                               "let every rank take the staged variant (MEGAMOE_DCU_USE_LARGE_OPT_3STAGE=1 or a larger "
-                               "dispatch_num_tokens)")
-        staged = True
 
     # argument checks of csrc/apis/mega_dcu.hpp:355-445
     if tuple(recipe) != (1, 1, 32):
@@ -535,7 +526,8 @@ def fp8_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer: SymmBuffer
             call_y.data_ptr(), w1.data_ptr(), l1_sf.contiguous().data_ptr(), w2.data_ptr(), l2_sf.contiguous().data_ptr(),
             stats_ptr, sb.buffer.data_ptr(), sb.route_scratch.data_ptr(), sb._peer_array, sb.rank, sb.num_ranks,
             sb.num_max_tokens_per_rank, e_loc, num_tokens, sb.num_topk, hidden, inter, clamp,
-            _lib.MODE_STAGED if staged else _lib.MODE_FUSED, runtime_ptr, _stream_ptr()))
+            (_lib.MODE_STAGED_SPLIT if sb._staged_split else _lib.MODE_STAGED) if staged else _lib.MODE_FUSED, runtime_ptr,
+            _stream_ptr()))
 
 
 fp8_w8a8_mega_moe = fp8_mega_moe

@@ -29,7 +29,8 @@ enum {
 enum {
     MM_SCR_STATUS = 0, MM_SCR_EPOCH, MM_SCR_PLAN, MM_SCR_BLOCK_COUNTS, MM_SCR_DEST_BASE, MM_SCR_EXPERT_TOTAL,
     MM_SCR_EXPERT_OFF, MM_SCR_MBLOCK_EXPERT, MM_SCR_MBLOCK_VALID, MM_SCR_DEST_ROW, MM_SCR_ROW_AMAX,
-    MM_SCR_ACT_SCALE, MM_SCR_ACT_BF16, MM_SCR_ACT_FP8, MM_SCR_ROUTE_BLOCKS, MM_SCR_NUM_OFFSETS
+    MM_SCR_ACT_SCALE, MM_SCR_ACT_BF16, MM_SCR_ACT_FP8, MM_SCR_SEND_BASE, MM_SCR_SEND_LIST, MM_SCR_L1_DONE, MM_SCR_L2_READY,
+    MM_SCR_GRID_SYNC, MM_SCR_ROUTE_BLOCKS, MM_SCR_NUM_OFFSETS
 };
 /* stages of one staged layer call, in launch order (indices of mm_get_stage_times) */
 enum {
@@ -38,7 +39,7 @@ enum {
     MM_STAGE_FUSED /* the single launch of MM_MODE_FUSED */, MM_NUM_STAGES
 };
 /* execution variants of mm_fp8_w8a8_mega_moe */
-enum { MM_MODE_STAGED = 0, MM_MODE_FUSED = 1 };
+enum { MM_MODE_STAGED = 0, MM_MODE_FUSED = 1, MM_MODE_STAGED_SPLIT = 2 };
 
 /* Message of the last failure on this thread. */
 const char* mm_last_error(void);
@@ -135,6 +136,12 @@ int mm_fp8_w8a8_mega_moe_static(void* y, const void* x_fp8, const float* x_sf, c
                                 int* stats, int num_tokens, int num_experts, int K, int H, int I, float activation_clamp,
                                 void* stream);
 
+/* Status words {code, phase, rank, expected, observed} of the LAST mm_fp8_w8a8_mega_moe_static call on the current device
+ * (they live inside the built-in work area, which the caller cannot address, and the next static call clears them): copies
+ * them to the host and synchronises the stream.  code 0 = no bounded wait expired and the receive pool did not overflow;
+ * otherwise y of that call is not valid.  No counterpart in the reference (see mm_read_status). */
+int mm_fp8_w8a8_mega_moe_static_status(void* stream, int32_t* out5);
+
 /* DeepEP-layout helpers of the reference's split baseline (DeepEP dispatch -> scatter -> grouped GEMM -> gather -> DeepEP
  * combine).  Scatter groups the received tokens by expert: expert_start_loc = exclusive prefix of
  * num_recv_tokens_per_expert; route (token, slot) with expert e gets row expert_start_loc[e] + its rank among e's routes (in
@@ -179,6 +186,13 @@ int mm_swiglu_quant_channelwise(const void* x_bf16, const float* weights, const 
  *   cta_pair: 0 = cta_group::1 MMAs, 1 = cta_group::2 MMAs (M256 over two SMs) as the CTA-pair GEMM kernels issue them.
  * status_dev: a zeroed device int. */
 int mm_fp8_mma_peak_probe(int iters, int operands, int cta_pair, int* status_dev, void* stream, double* flops_out);
+
+/* Measurement aid (no counterpart in the reference, whose test divides by a datasheet interconnect figure,
+ * tests/test_mega_moe_dcu.py:20-22): write bytes_per_dst bytes (a multiple of 512) with plain 16-byte vector stores into
+ * each of the n_dst device addresses of the HOST array dst_ptrs.  With peer-mapped addresses (e.g. the receive pool of
+ * other ranks' symmetric buffers, between layer calls) and events on `stream` this gives the NVLink store rate that the
+ * dispatch push and the GEMM2 combine stores can at best reach.  The destinations' previous contents are lost. */
+int mm_peer_store_probe(const uint64_t* dst_ptrs, int n_dst, int64_t bytes_per_dst, void* stream);
 
 /* Per-stage device timing of the layer call (the reference's test prints per-kernel times with a profiler,
  * tests/test_mega_moe_dcu.py:794-834; here CUDA events are recorded on the caller's stream around every launch).

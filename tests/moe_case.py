@@ -69,10 +69,27 @@ def run_oracle(case: Case, clamp=None, variant="fused", trace=False):
                          case.E, clamp, variant, trace=trace)
 
 
+def poison_work_buffers(sb) -> None:
+    """Fill everything a layer call is supposed to WRITE before it reads -- receive pool rows and their metadata, the
+    combine buffer, the bf16 and FP8 activations -- with all-ones bytes (NaN as e4m3 and as bf16, -1 as metadata), so that
+    a row, a slot or a tile the call fails to write cannot be masked by what an earlier call left there.  The reference
+    has the same aid: DG_COMM_KERNEL_DEBUG clears its symmetric buffer after every call (csrc/apis/mega.hpp:221-224).
+    Enqueued on the current stream right before the call: peers write into this rank's pool and combine buffer only after
+    this rank has entered the call (they wait for its route counts first)."""
+    for name, view in (("pool_x", sb.symm_view), ("pool_meta", sb.symm_view), ("combine", sb.symm_view),
+                       ("act_bf16", sb.scratch_view), ("act_fp8", sb.scratch_view)):
+        nbytes = {"pool_x": sb.pool_rows * sb.hidden, "pool_meta": sb.pool_rows * 16,
+                  "combine": sb.num_topk * sb.num_max_tokens_per_rank * sb.hidden * 2,
+                  "act_bf16": sb.pool_rows * sb.intermediate_hidden * 2, "act_fp8": sb.pool_rows * sb.intermediate_hidden}[name]
+        view(name, (nbytes,), torch.uint8).fill_(0xFF)
+
+
 def run_cuda_rank(case: Case, rank: int, group=None, clamp=None, t_max: Optional[int] = None, stats=None,
-                  marlin=False, sb=None, keep=False, quantise_on_device=True, variant=None, **kwargs):
+                  marlin=False, sb=None, keep=False, quantise_on_device=True, variant=None, poison=True, **kwargs):
     """Run one rank of the case on the current CUDA device through the megamoe API. Returns (y, sym_buffer|None).
-    variant: None = the API's token-threshold choice, "fused" / "staged" = force that kernel variant."""
+    variant: None = the API's token-threshold choice; "fused" / "staged" = force that kernel variant ("staged" = routing
+    kernels + the layer kernel with in-kernel NVLink push); "split" = the staged variant as separate dispatch / GEMM1 /
+    requantisation / GEMM2 launches."""
     import megamoe
     dev = torch.device("cuda", torch.cuda.current_device())
     T = case.tokens[rank]
@@ -81,7 +98,8 @@ def run_cuda_rank(case: Case, rank: int, group=None, clamp=None, t_max: Optional
     if own:
         sb = megamoe.get_symm_buffer_for_mega_moe(group, case.E, t_cap, case.K, case.H, case.I)
     if variant is not None:
-        sb._large_opt_3stage_mode = {"fused": "off", "staged": "force"}[variant]
+        sb._large_opt_3stage_mode = {"fused": "off", "staged": "force", "split": "force"}[variant]
+        sb._staged_split = variant == "split"
     if quantise_on_device:
         w1 = megamoe.transform_fp8_weights_for_mega_moe(case.w1_bf16[rank].to(dev), case.w2_bf16[rank].to(dev),
                                                         layout="marlin" if marlin else "tiled")
@@ -96,6 +114,8 @@ def run_cuda_rank(case: Case, rank: int, group=None, clamp=None, t_max: Optional
     sb.x[:T].copy_(xq); sb.x_sf[:T].copy_(xs)
     sb.topk_idx[:T].copy_(case.idx[rank].to(dev)); sb.topk_weights[:T].copy_(case.w[rank].to(dev))
     y = torch.full((T, case.H), float("nan"), dtype=torch.bfloat16, device=dev)
+    if poison:
+        poison_work_buffers(sb)
     megamoe.fp8_w8a8_mega_moe(y, l1, l2, sb, cumulative_local_expert_recv_stats=stats, activation_clamp=clamp, **kwargs)
     sb.check_status()
     if own and not keep:

@@ -98,21 +98,19 @@ def test_python_api_surface_and_selector():
         assert megamoe._large_opt_3stage_selected(int(n), str(mode), 128) == bool(want)
 
 
-def test_variant_choice_is_the_same_on_every_rank():
-    """Ranks with different token counts must agree on staged vs fused: with several ranks the choice uses the buffer
-    capacity (or the caller's dispatch_num_tokens), never the rank's own token count."""
+def test_variant_choice_follows_the_reference_rule():
+    """Staged above the token threshold, decided on dispatch_num_tokens if given, else on the rows of y -- the rule of the
+    reference (megamoe/__init__.py:398-404).  Ranks holding different token counts agree by passing one
+    dispatch_num_tokens, as the reference asks of its callers."""
     from deepgemm_b200.megamoe import _eager_variant_is_staged as sel
-    # one rank: the call's own token count decides (reference rule: staged above the threshold)
-    assert sel(1, "auto", 128, 7, None, 4096, 6) is False
-    assert sel(1, "auto", 128, 133, None, 4096, 6) is True
-    # two ranks holding 133 and 7 tokens in a 133-token buffer agree
-    assert sel(2, "auto", 128, 133, None, 133, 4) == sel(2, "auto", 128, 7, None, 133, 4) is True
-    assert sel(2, "auto", 128, 100, None, 128, 4) == sel(2, "auto", 128, 0, None, 128, 4) is False
-    # an explicit dispatch_num_tokens (the same on every rank) wins
-    assert sel(2, "auto", 128, 7, 133, 4096, 4) is True and sel(2, "auto", 128, 133, 64, 4096, 4) is False
-    # forced modes ignore the counts; more routes than the fused kernel holds fall back to staged in auto mode
-    assert sel(2, "force", 128, 1, None, 8, 2) is True and sel(2, "off", 128, 4096, None, 4096, 6) is False
-    assert sel(1, "auto", 100000, 2000, None, 4096, 6) is True
+    assert sel("auto", 128, 7, None) is False
+    assert sel("auto", 128, 133, None) is True
+    assert sel("auto", 128, 128, None) is False                      # at the threshold: still fused
+    # an explicit dispatch_num_tokens (the same on every rank) wins over the rank's own count
+    assert sel("auto", 128, 7, 133) is True and sel("auto", 128, 133, 64) is False
+    assert sel("auto", 128, 133, 0) is False
+    # forced modes ignore the counts; there is no route ceiling on the fused variant any more
+    assert sel("force", 128, 1, None) is True and sel("off", 128, 100000, None) is False
 
 
 def test_packed_weight_cache_is_bound_to_the_tensor_object():

@@ -119,7 +119,7 @@ def test_input_cast_bit_exact_random_and_edges():
     assert torch.equal(q.cpu().view(torch.uint8), q_ref.view(torch.uint8))
 
 
-@pytest.mark.parametrize("variant", ["staged", "fused"])
+@pytest.mark.parametrize("variant", ["staged", "fused", "split"])
 def test_small_config_literal_bar(variant):
     """256 tokens, hidden 512, intermediate 256, 8 experts, top-2, seed 0 (the CPU-runnable configuration)."""
     _check_case(mc.make_case(1, 8, 2, 512, 256, [256], seed=0), literal_bar=True, variant=variant)
@@ -130,7 +130,8 @@ def test_fused_and_staged_variants_are_bitwise_identical():
     case = mc.make_case(1, 16, 4, 512, 256, [300], seed=14, invalid_fraction=0.1)
     a, _ = mc.run_cuda_rank(case, 0, variant="staged", clamp=10.0)
     b, _ = mc.run_cuda_rank(case, 0, variant="fused", clamp=10.0)
-    assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+    c, _ = mc.run_cuda_rank(case, 0, variant="split", clamp=10.0)
+    assert torch.equal(a.view(torch.int16), b.view(torch.int16)) and torch.equal(a.view(torch.int16), c.view(torch.int16))
 
 
 @pytest.mark.parametrize("tokens,invalid", [(0, 0.0), (1, 0.0), (33, 0.3), (512, 0.0)])
@@ -149,16 +150,49 @@ def test_fused_variant_dsv4_shaped_slice_and_reuse():
     assert torch.equal(y.view(torch.int16), y2.view(torch.int16)) and torch.equal(y.view(torch.int16), y3.view(torch.int16))
 
 
-def test_fused_variant_refuses_more_routes_than_it_can_hold():
+def test_fused_variant_has_no_route_ceiling_and_graph_bucket_may_exceed_the_tokens():
+    """The fused kernel numbers its routes from per-CTA counts, not from a shared-memory list, so any token count up to
+    the buffer capacity runs fused -- eagerly and as a graph bucket whose device-side token count is much smaller than
+    the bucket (8192-token bucket, 128 live tokens: the decode configuration)."""
     import megamoe
-    from deepgemm_b200 import _lib
-    case = mc.make_case(1, 8, 2, 512, 256, [16], seed=16)
-    sb = megamoe.get_symm_buffer_for_mega_moe(None, 8, 4000, 2, 512, 256)
-    l1, l2 = megamoe.transform_fp8_weights_for_mega_moe(case.w1_bf16[0].cuda(), case.w2_bf16[0].cuda())
-    y = torch.empty((4000, 512), dtype=torch.bfloat16, device="cuda")
-    with pytest.raises(_lib.MegaMoeError):          # graph mode bounds the routes by the buffer capacity: 4224 * 2 > 4096
-        megamoe.fp8_mega_moe(y, l1, l2, sb, big_fused_cuda_graph=True)
+    case = mc.make_case(1, 8, 2, 512, 256, [3000], seed=16, invalid_fraction=0.05)
+    _check_case(case, variant="fused")                                  # 6000 routes in one fused launch
+    small = mc.make_case(1, 8, 2, 512, 256, [128], seed=17)
+    ys, _, _ = mc.run_oracle(small)
+    sb = megamoe.get_symm_buffer_for_mega_moe(None, 8, 8192, 2, 512, 256)
+    l1, l2 = megamoe.transform_fp8_weights_for_mega_moe(small.w1_bf16[0].cuda(), small.w2_bf16[0].cuda())
+    xq, xs = megamoe.cast_to_fp8_channelwise(small.x_bf16[0].cuda())
+    sb.x[:128].copy_(xq); sb.x_sf[:128].copy_(xs); sb.topk_idx[:128].copy_(small.idx[0].cuda()); sb.topk_weights[:128].copy_(small.w[0].cuda())
+    y = torch.full((8192, 512), 7.0, dtype=torch.bfloat16, device="cuda")
+    sb.cuda_graph_num_tokens.fill_(128)
+    megamoe.fp8_mega_moe(y, l1, l2, sb, big_fused_cuda_graph=True)
+    sb.check_status()
+    mc.assert_layer_close(y[:128].cpu(), ys[0], "fused, 8192-token bucket, 128 live tokens")
+    assert bool((y[128:] == 7.0).all())
     sb.destroy()
+
+
+def test_device_side_token_count_is_clamped_to_the_rows_of_y():
+    """A stale or oversized cuda_graph_num_tokens must never make a kernel write past the bucket: with a 96-row bucket in a
+    384-token buffer and a device-side count of 200, rows 96.. of a larger allocation stay untouched and the first 96
+    rows are the 96-token result (deep_gemm/include/deep_gemm/impls/mega_moe_dcu.cuh:292 clamps the same way)."""
+    import megamoe
+    case = mc.make_case(1, 8, 2, 512, 256, [96], seed=18)
+    ys, _, _ = mc.run_oracle(case)
+    for flag in (dict(stages_fused_cuda_graph=True), dict(big_fused_cuda_graph=True)):
+        sb = megamoe.get_symm_buffer_for_mega_moe(None, 8, 96, 2, 512, 256)      # capacity 384, bucket 96
+        l1, l2 = megamoe.transform_fp8_weights_for_mega_moe(case.w1_bf16[0].cuda(), case.w2_bf16[0].cuda())
+        xq, xs = megamoe.cast_to_fp8_channelwise(case.x_bf16[0].cuda())
+        sb.x[:96].copy_(xq); sb.x_sf[:96].copy_(xs); sb.topk_idx[:96].copy_(case.idx[0].cuda()); sb.topk_weights[:96].copy_(case.w[0].cuda())
+        sb.topk_idx[96:].fill_(3); sb.topk_weights[96:].fill_(0.5)              # live-looking routes past the bucket
+        big = torch.full((384, 512), 7.0, dtype=torch.bfloat16, device="cuda")
+        y = big[:96]
+        sb.cuda_graph_num_tokens.fill_(200)
+        megamoe.fp8_mega_moe(y, l1, l2, sb, **flag)
+        sb.check_status()
+        assert bool((big[96:] == 7.0).all()), f"{flag}: rows past the bucket were written"
+        mc.assert_layer_close(y.cpu(), ys[0], f"{flag}: clamped to the bucket")
+        sb.destroy()
 
 
 @pytest.mark.parametrize("clamp", [10.0, 1.0])
@@ -197,11 +231,11 @@ def test_cta_pair_gemms_match_the_single_cta_kernels(shape, monkeypatch):
     E, K, H, I, T, zipf = shape
     case = mc.make_case(1, E, K, H, I, [T], seed=21, zipf=zipf, invalid_fraction=0.05)
     monkeypatch.setenv("MEGAMOE_GEMM_PAIR", "0")
-    a, _ = mc.run_cuda_rank(case, 0, variant="staged", clamp=10.0)
+    a, _ = mc.run_cuda_rank(case, 0, variant="split", clamp=10.0)
     monkeypatch.setenv("MEGAMOE_GEMM_PAIR", "1")
-    b, _ = mc.run_cuda_rank(case, 0, variant="staged", clamp=10.0)
+    b, _ = mc.run_cuda_rank(case, 0, variant="split", clamp=10.0)
     assert torch.equal(a.view(torch.int16), b.view(torch.int16))
-    _check_case(case, clamp=10.0, variant="staged")
+    _check_case(case, clamp=10.0, variant="split")
 
 
 def test_marlin_weights_and_stats_accumulate():

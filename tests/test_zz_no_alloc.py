@@ -34,6 +34,9 @@ def _static_call(lib, case, clamp):
         s2.data_ptr(), stats.data_ptr(), T, case.E, case.K, case.H, case.I, float("inf") if clamp is None else clamp,
         torch.cuda.current_stream().cuda_stream))
     torch.cuda.synchronize()
+    out = (ctypes.c_int32 * 5)()
+    _lib.check(lib.mm_fp8_w8a8_mega_moe_static_status(torch.cuda.current_stream().cuda_stream, out))
+    assert out[0] == 0, f"a bounded wait expired inside the static call: {list(out)}"
     return y.cpu(), stats.cpu()
 
 
@@ -49,6 +52,37 @@ def test_static_work_area_variant_matches_regular_entry_point(built_lib):
         assert torch.equal(y.view(torch.int16), y_ref.view(torch.int16)), "static variant differs from the regular entry point"
         assert torch.equal(stats, stats_ref.cpu())
         mc.assert_layer_close(y, mc.run_oracle(case, clamp)[0][0], "static variant vs oracle")
+
+
+def test_static_variant_leaves_free_device_memory_unchanged(built_lib):
+    """What the entry point is for: a caller whose arena owns all of HBM.  Once the kernels' code is resident (first
+    call), further calls must not take or give back a single byte of device memory."""
+    if not torch.cuda.is_available():
+        pytest.fail("needs a CUDA device")
+    import megamoe
+    from deepgemm_b200 import _lib
+    dev = torch.device("cuda")
+    case = mc.make_case(1, 8, 2, 512, 256, [200], seed=42)
+    (w1, s1), (w2, s2) = megamoe.transform_fp8_weights_for_mega_moe(case.w1_bf16[0].to(dev), case.w2_bf16[0].to(dev))
+    xq, xs = megamoe.cast_to_fp8_channelwise(case.x_bf16[0].to(dev))
+    idx, w = case.idx[0].to(dev).contiguous(), case.w[0].to(dev).contiguous()
+    y = torch.empty((200, case.H), dtype=torch.bfloat16, device=dev)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def call():
+        _lib.check(built_lib.mm_fp8_w8a8_mega_moe_static(
+            y.data_ptr(), xq.data_ptr(), xs.data_ptr(), idx.data_ptr(), w.data_ptr(), w1.data_ptr(), s1.data_ptr(), w2.data_ptr(),
+            s2.data_ptr(), None, 200, case.E, case.K, case.H, case.I, float("inf"), stream))
+        torch.cuda.synchronize()
+
+    call()                                              # loads the kernels' code, resolves the work area's address
+    free_before, _ = torch.cuda.mem_get_info()
+    for _ in range(3):
+        call()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before, f"free device memory changed across static calls: {free_before} -> {free_after}"
+    y_ref, _ = mc.run_cuda_rank(case, 0)                 # regular entry point with its own buffers: the same bits
+    assert torch.equal(y.cpu().view(torch.int16), y_ref.view(torch.int16)), "static variant differs from the regular entry point"
 
 
 def test_static_variant_refuses_shapes_beyond_its_work_area(built_lib):

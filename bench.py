@@ -478,8 +478,9 @@ def main():
     if args.variant != "auto":
         sb._large_opt_3stage_mode = {"fused": "off", "staged": "force", "split": "force"}[args.variant]
         sb._staged_split = args.variant == "split"
+        sb._staged_split_auto = False
     staged = megamoe._large_opt_3stage_selected(T, sb._large_opt_3stage_mode, sb._large_opt_3stage_threshold)
-    variant = ("staged-split" if sb._staged_split else "staged") if staged else "fused"
+    variant = ("staged-split" if megamoe._staged_as_split_launches(sb, T, e_loc) else "staged") if staged else "fused"
     y = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
     stream = torch.cuda.current_stream().cuda_stream
     lib = _lib.lib()
@@ -680,7 +681,8 @@ def main():
         # ---- exposed communication: the step minus its all-local twin (this rank's experts only, the same token count and
         #      top-k, one rank, no peer traffic), measured in the same run on every GPU at once
         twin = megamoe.get_symm_buffer_for_mega_moe(None, e_loc, T, K, H, I)
-        twin._large_opt_3stage_mode, twin._staged_split = sb._large_opt_3stage_mode, sb._staged_split
+        twin._large_opt_3stage_mode = sb._large_opt_3stage_mode
+        twin._staged_split, twin._staged_split_auto = megamoe._staged_as_split_launches(sb, T, e_loc), False
         g = torch.Generator(device=dev).manual_seed(77 + rank)
         tw_, ti_ = torch.topk(torch.softmax(torch.randn((T, e_loc), generator=g, device=dev), dim=-1), K, dim=-1)
         twin.x[:T].copy_(sb.x[:T]); twin.x_sf[:T].copy_(sb.x_sf[:T])

@@ -563,7 +563,8 @@ int mm_fp8_w8a8_mega_moe(void* y, const void* w1, const float* s1, const void* w
     fp.send_list = reinterpret_cast<const int4*>(sc + rp.cl.send_list);
     fp.act_fp8 = sc + rp.cl.act_fp8;
     fp.act_scale_w = reinterpret_cast<float*>(sc + rp.cl.act_scale);
-    // a wave holds enough GEMM1 tiles for about two rounds over the SMs, so its requantisation is done when its GEMM2 starts
+    // a wave holds enough GEMM1 tiles for about two rounds over the SMs; its GEMM2 tiles come up kWaveLookahead waves later,
+    // by when its requantisation is done
     fp.wave_mblocks = (2 * sms + g1.n_blocks - 1) / g1.n_blocks;
     static const int wave_override = [] { const char* v = getenv("MEGAMOE_WAVE_MBLOCKS"); return v ? atoi(v) : 0; }();   // tuning aid
     if (wave_override != 0) fp.wave_mblocks = wave_override > 0 ? wave_override : (1 << 28);
@@ -586,11 +587,11 @@ int mm_fp8_w8a8_mega_moe(void* y, const void* w1, const float* s1, const void* w
     //                         launch, so that the transfers overlap the tensor work expert by expert;
     //   MM_MODE_STAGED_SPLIT  dispatch, a cross-rank barrier, GEMM1, requantisation and GEMM2 as separate launches.
     if (int rc = stage_begin(stream)) return rc;
+    int* reset_a = nullptr; int* reset_b = nullptr;
+    int reset_a_words = 0, reset_b_words = 0;
 #define MM_STAGE(id) do { MM_LAUNCHED(); if (int rc_ = stage_end(id, stream)) return rc_; } while (0)
-    mm::route_count_kernel<<<route_blocks, MM_ROUTE_CHUNK, 0, stream>>>(rp);
+    mm::route_count_kernel<<<route_blocks, 1024, 0, stream>>>(rp);     // its last block also exchanges the counts
     MM_STAGE(MM_STAGE_ROUTE_COUNT);
-    mm::route_exchange_kernel<<<1, 1024, 0, stream>>>(rp);
-    MM_STAGE(MM_STAGE_ROUTE_EXCHANGE);
     mm::route_plan_kernel<<<1, 1024, 0, stream>>>(rp);
     MM_STAGE(MM_STAGE_ROUTE_PLAN);
     if (mode == MM_MODE_STAGED) {
@@ -600,12 +601,13 @@ int mm_fp8_w8a8_mega_moe(void* y, const void* w1, const float* s1, const void* w
         MM_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(mm::mega_moe_fused_kernel), dim3(sms), dim3(mm::kFusedThreads),
                                             fused_args, mm::kGemmSmemBytes, stream));
         MM_STAGE(MM_STAGE_FUSED);
-        // Leave the per-m-block dependency counters zero for the next call.  l1_done, l2_ready and grid_sync are adjacent;
-        // the arrival counters live in the symmetric buffer: peers bump them again only after every rank has entered its
-        // next call (they wait for its route counts first), which on this stream comes after this memset.
+        // the reduce kernel below leaves the per-m-block dependency counters zero for the next call: l1_done, l2_ready and
+        // grid_sync are adjacent in the scratch buffer, the arrival counters live in the symmetric buffer
         const int64_t n_mb = rp.sl.pool_rows / MM_BLOCK_M;
-        MM_CUDA(cudaMemsetAsync(sc + rp.cl.l1_done, 0, (size_t)(rp.cl.grid_sync + 32 - rp.cl.l1_done), stream));
-        MM_CUDA(cudaMemsetAsync(rp.sym + rp.sl.pool_arrive, 0, (size_t)(n_mb + 1) * sizeof(int), stream));
+        reset_a = reinterpret_cast<int*>(sc + rp.cl.l1_done);
+        reset_a_words = (int)((rp.cl.grid_sync + 32 - rp.cl.l1_done) / 4);
+        reset_b = reinterpret_cast<int*>(rp.sym + rp.sl.pool_arrive);
+        reset_b_words = (int)(n_mb + 1);
     } else {
     mm::dispatch_kernel<<<route_blocks, mm::MM_DISPATCH_THREADS, 0, stream>>>(rp);
     MM_STAGE(MM_STAGE_DISPATCH);
@@ -648,7 +650,8 @@ int mm_fp8_w8a8_mega_moe(void* y, const void* w1, const float* s1, const void* w
         MM_STAGE(MM_STAGE_BARRIER_COMBINE);
     }
     mm::combine_reduce_kernel<<<sms * 8, 256, 0, stream>>>(rp.sym, rp.sl, E, T_max, K, H, num_tokens, runtime_num_tokens,
-                                                          static_cast<__nv_bfloat16*>(y), g1.status);
+                                                          static_cast<__nv_bfloat16*>(y), g1.status, reset_a, reset_a_words,
+                                                          reset_b, reset_b_words);
     MM_STAGE(MM_STAGE_REDUCE);
 #undef MM_STAGE
     return 0;

@@ -23,7 +23,7 @@
 //     rows are still crossing NVLink.  The combine barrier, the reduce and the counter reset are launches after it.
 //
 // Step 4, the tile loop: m-blocks are grouped in waves; with G1(k) / G2(k) = all GEMM1 / GEMM2 tiles of wave k the
-// order is  G1(0), G1(1), [G1(2), G2(0)], [G1(3), G2(1)], ..., G2(n-1)  (round-robin over CTAs), so the tensor-bound
+// order is  G1(0), G1(1), G1(2), [G1(3), G2(0)], [G1(4), G2(1)], ..., G2(n-1)  (round-robin over CTAs), so the tensor-bound
 // GEMM1 work overlaps the NVLink-bound combine stores of GEMM2.  Dependencies are per m-block, never global barriers:
 //   - GEMM1 tile: weights start streaming at once; the token operand waits for arrive[m-block] == valid rows; each
 //     epilogue warp counts its stored share in l1_done[m-block];
@@ -44,6 +44,8 @@ constexpr int kHelperWarps = 2;
 constexpr int kFusedFirstEpilogueWarp = 2 + kHelperWarps;                    // a multiple of 4: warp & 3 == TMEM lane quarter
 constexpr int kFusedThreads = (kFusedFirstEpilogueWarp + kEpilogueWarps) * 32;
 constexpr int kPushChunk = 8;             // rows a helper warp claims, pushes and signals at a time
+constexpr int kPushChunkStart = 2;        // ... at kernel start, when every warp of the grid pushes at once: small chunks let the
+                                          // first m-blocks complete (and the first GEMM1 tiles start) several microseconds earlier
 static_assert(kFusedFirstEpilogueWarp % 4 == 0, "epilogue warps must start at a multiple of four");
 
 // words of the `plan` array in the scratch buffer (written by route_plan_kernel or by this kernel's step 2)
@@ -97,6 +99,9 @@ __device__ __forceinline__ bool wait_flag_ge(const int* flag, int target, bool s
 }
 
 // Position of a tile index in the wave order.  A CTA's tile indices grow, so seek() only moves forward.
+// Groups: G1(0) .. G1(L-1), then pairs G1(k+L), G2(k) with L = kWaveLookahead: a wave's requantisation has L waves of
+// GEMM1 tiles (about 2 L rounds over the SMs) to finish before its GEMM2 tiles come up.
+constexpr int kWaveLookahead = 3;
 struct WaveOrder {
     enum { kG1 = 0, kG2 = 1 };
     int n_waves, wave_m, num_mblocks, nb1, nb2;
@@ -105,12 +110,12 @@ struct WaveOrder {
         : n_waves((num_mblocks_ + wave_m_ - 1) / wave_m_), wave_m(wave_m_), num_mblocks(num_mblocks_), nb1(nb1_), nb2(nb2_),
           g(0), base(0) { set(); }
     __device__ __forceinline__ int wave_mblocks(int w) const { return w < n_waves ? min(wave_m, num_mblocks - w * wave_m) : 0; }
-    __device__ __forceinline__ void set() {      // groups: G1(0), G1(1), then pairs G1(k+2), G2(k)
-        if (g < 2) { kind = kG1; wave = g; }
+    __device__ __forceinline__ void set() {
+        if (g < kWaveLookahead) { kind = kG1; wave = g; }
         else {
-            const int k = (g - 2) >> 1, j = (g - 2) & 1;
+            const int k = (g - kWaveLookahead) >> 1, j = (g - kWaveLookahead) & 1;
             kind = j == 0 ? kG1 : kG2;
-            wave = j == 0 ? k + 2 : k;
+            wave = j == 0 ? k + kWaveLookahead : k;
         }
         size = wave_mblocks(wave) * (kind == kG1 ? nb1 : nb2);
     }
@@ -152,13 +157,13 @@ __device__ __forceinline__ void push_two_rows(const uint8_t* src0, uint8_t* dst0
 // One chunk of the send list (helper warps, gemm_only): copy up to kPushChunk rows into their owners' receive pools, write
 // their metadata, then -- warp barrier, one system-scope fence -- count one arrival per row on the owner (per m-block and
 // in total).
-__device__ __forceinline__ void push_chunk(const FusedParams& fp, int j0, int n_send, int lane) {
+__device__ __forceinline__ void push_chunk(const FusedParams& fp, int j0, int chunk, int n_send, int lane) {
     const RouteParams& rp = fp.rp;
     const float* tw = reinterpret_cast<const float*>(rp.sym + rp.sl.topk_weights);
     const float* x_sf = reinterpret_cast<const float*>(rp.sym + rp.sl.x_sf);
     const uint8_t* x = rp.sym + rp.sl.x;
     const int arrive_total_slot = static_cast<int>(rp.sl.pool_rows / MM_BLOCK_M);
-    const int n = min(kPushChunk, n_send - j0);
+    const int n = min(chunk, n_send - j0);
     // lane j < n describes row j of the chunk
     int route = -1, row = -1, owner = 0, token = 0;
     if (lane < n) {
@@ -496,14 +501,15 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
     const int* arrive = reinterpret_cast<const int*>(rp.sym + rp.sl.pool_arrive);
 
     if (warp == 0) {
-        // -------------------------------------------------------------- TMA producer
+        // -------------------------------------------------------------- TMA producer (one thread)
+        if (lane == 0) {
         int stage = 0; uint32_t phase = 0;
         bool alive = true;
         // once every row has arrived (every m-block is requantised) no further per-tile polling is needed
         bool all_arrived = false, all_ready = false;
         WaveOrder order = order_init;
         int local_i = -1;                                   // index of the tile in this CTA's sequence
-        uint64_t polled_g1 = 0, polled_g2 = 0;              // time this warp itself spent polling for GEMM1 / GEMM2 tiles (tuning aid)
+        uint64_t polled_g1 = 0, polled_g2 = 0;              // time this thread itself spent polling for GEMM1 / GEMM2 tiles (tuning aid)
         for (int tile = blockIdx.x; tile < tiles_all && alive; tile += gridDim.x) {
             int kind, mb, nb;
             order.seek(tile, kind, mb, nb);
@@ -518,33 +524,31 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
             for (int kb = 0; kb < k_blocks; ++kb) {
                 if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, g.timeout_ns)) { alive = false; break; }
                 const uint32_t a_dst = smem_base + stage * kStageBytes;
-                if (lane == 0) {
-                    mbar_arrive_expect_tx(full_bar(stage), kStageBytes);
-                    tma_load_2d(a_dst + kABytes, tb, 0, (b_tile0 + kb) * kBlockN, full_bar(stage));   // weights first
-                }
-                // The token operand of this m-block must be complete before TMA may read it.  Normally the scout (an epilogue
-                // lane that polls ahead while it waits for accumulators) has confirmed that already, and this warp, whose
-                // loads the tensor pipe is waiting for, only reads a shared-memory word; otherwise it polls itself.
-                if (kb == 0 && local_i >= *reinterpret_cast<volatile int*>(s_misc + 4) && !(second ? all_ready : all_arrived)) {
-                    int seen = 0;
-                    bool ok = true;
-                    const uint64_t t_poll = global_timer_ns();
-                    if (second) {
-                        all_ready = ld_acquire_gpu(fp.grid_sync + 2) - requant_units >= 0;
-                        if (!all_ready) ok = wait_flag_ge(fp.l2_ready + mb, 4, false, status, g.timeout_ns, &seen);
-                    } else {
-                        all_arrived = ld_acquire_sys(arrive + arrive_total_slot) - rows_expected >= 0;
-                        if (!all_arrived) ok = wait_flag_ge(arrive + mb, g.mblock_valid[mb], true, status, rp.barrier_timeout_ns, &seen);
-                    }
-                    if (second) polled_g2 += global_timer_ns() - t_poll; else polled_g1 += global_timer_ns() - t_poll;
-                    if (!ok) {
-                        if (lane == 0) report_status(rp.scratch, rp.cl, MM_ERR_GRID_BARRIER_TIMEOUT, second ? 2 : 1, mb,
-                                                     second ? 4 : g.mblock_valid[mb], seen);
-                        *abort_flag = 1;
-                        alive = false;
-                    }
-                }
+                mbar_arrive_expect_tx(full_bar(stage), kStageBytes);
+                tma_load_2d(a_dst + kABytes, tb, 0, (b_tile0 + kb) * kBlockN, full_bar(stage));   // weights first
                 if (kb == 0) {
+                    // The token operand of this m-block must be complete before TMA may read it.  Normally the scout (an
+                    // epilogue lane that polls ahead while it waits for accumulators) has confirmed that already, and this
+                    // thread, whose loads the tensor pipe is waiting for, only reads a shared-memory word; otherwise it polls.
+                    const bool confirmed = local_i < *reinterpret_cast<volatile int*>(s_misc + 4);
+                    if (!confirmed && !(second ? all_ready : all_arrived)) {
+                        int seen = 0;
+                        bool ok = true;
+                        const uint64_t t_poll = global_timer_ns();
+                        if (second) {
+                            all_ready = ld_acquire_gpu(fp.grid_sync + MM_SYNC_UNITS_DONE) - requant_units >= 0;
+                            if (!all_ready) ok = wait_flag_ge(fp.l2_ready + mb, 4, false, status, g.timeout_ns, &seen);
+                        } else {
+                            all_arrived = ld_acquire_sys(arrive + arrive_total_slot) - rows_expected >= 0;
+                            if (!all_arrived) ok = wait_flag_ge(arrive + mb, g.mblock_valid[mb], true, status, rp.barrier_timeout_ns, &seen);
+                        }
+                        if (second) polled_g2 += global_timer_ns() - t_poll; else polled_g1 += global_timer_ns() - t_poll;
+                        if (!ok) {
+                            report_status(rp.scratch, rp.cl, MM_ERR_GRID_BARRIER_TIMEOUT, second ? 2 : 1, mb, second ? 4 : g.mblock_valid[mb], seen);
+                            *abort_flag = 1;
+                            alive = false;
+                        }
+                    }
                     // rows were written with ordinary stores (by other SMs or GPUs) and their completion was observed with an
                     // acquire load (here, or by the scout, whose result came through shared memory): order all that before
                     // the TMA reads
@@ -552,18 +556,18 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
                     asm volatile("fence.proxy.async;" ::: "memory");
                 }
                 // issue the token tile even on failure so that the stage's byte count completes and nobody is left waiting
-                if (lane == 0) tma_load_2d(a_dst, ta, kb * kBlockK, mb * kBlockM, full_bar(stage));
-                __syncwarp();
+                tma_load_2d(a_dst, ta, kb * kBlockK, mb * kBlockM, full_bar(stage));
                 if (++stage == kStages) { stage = 0; phase ^= 1u; }
                 if (!alive) break;
             }
         }
-        if (lane == 0) {
-            stamp(7);
-            if (blockIdx.x == 0) { status[14] = static_cast<int>(polled_g1 / 100); status[15] = static_cast<int>(polled_g2 / 100); }
+        stamp(7);
+        if (blockIdx.x == 0) { status[14] = static_cast<int>(polled_g1 / 100); status[15] = static_cast<int>(polled_g2 / 100); }
         }
+        __syncwarp();
     } else if (warp == 1) {
-        // -------------------------------------------------------------- MMA issuer
+        // -------------------------------------------------------------- MMA issuer (one thread)
+        if (lane == 0) {
         constexpr uint32_t idesc = umma_idesc_f8(kBlockM, kBlockN);
         int stage = 0; uint32_t phase = 0;
         int acc = 0; uint32_t acc_phase = 0;
@@ -580,21 +584,20 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
             for (int kb = 0; kb < k_blocks; ++kb) {
                 if (!mbar_wait(full_bar(stage), phase, abort_flag, g.timeout_ns)) { alive = false; break; }
                 tc_fence_after();
-                if (lane == 0) {
-                    const uint32_t a_src = smem_base + stage * kStageBytes;
-                    const uint64_t da = umma_desc_k_sw128(a_src);
-                    const uint64_t db = umma_desc_k_sw128(a_src + kABytes);
+                const uint32_t a_src = smem_base + stage * kStageBytes;
+                const uint64_t da = umma_desc_k_sw128(a_src);
+                const uint64_t db = umma_desc_k_sw128(a_src + kABytes);
 #pragma unroll
-                    for (int k = 0; k < kBlockK / 32; ++k) umma_f8(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
-                    umma_commit(empty_bar(stage));
-                    if (kb == k_blocks - 1) umma_commit(tfull_bar(acc));
-                }
-                __syncwarp();
+                for (int k = 0; k < kBlockK / 32; ++k) umma_f8(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                umma_commit(empty_bar(stage));
+                if (kb == k_blocks - 1) umma_commit(tfull_bar(acc));
                 if (++stage == kStages) { stage = 0; phase ^= 1u; }
             }
             if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
         }
-        if (lane == 0) stamp(8);
+        stamp(8);
+        }
+        __syncwarp();
     } else if (warp < kFusedFirstEpilogueWarp) {
         // -------------------------------------------------------------- helpers
         // Two jobs:
@@ -614,12 +617,13 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
         // (a) push: walk the send list until it is exhausted (policy bit 0 clear: only warp 2 of a CTA pushes once several
         //     ranks are involved, so that warp 3 requantises from the start and GEMM2 tiles never wait for the link)
         const bool pusher = (fp.policy & 1) != 0 || rp.R == 1 || warp == 2;
-        while (pusher) {
+        for (int it = 0; pusher; ++it) {
+            const int chunk = it < 2 ? kPushChunkStart : kPushChunk;
             int j0 = 0;
-            if (lane == 0) j0 = atomicAdd(fp.grid_sync + MM_SYNC_PUSH_HEAD, kPushChunk);
+            if (lane == 0) j0 = atomicAdd(fp.grid_sync + MM_SYNC_PUSH_HEAD, chunk);
             j0 = __shfl_sync(0xffffffffu, j0, 0);
             if (j0 >= n_send) break;
-            push_chunk(fp, j0, n_send, lane);
+            push_chunk(fp, j0, chunk, n_send, lane);
         }
         if (warp == 2 && lane == 0) stamp(12);
         // (b) requantisation: claim the units in order and wait for each
@@ -658,10 +662,10 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
             const int n_send = fp.plan[MM_PLAN_SEND];
             while (true) {
                 int j0 = n_send;
-                if (lane == 0 && !mbar_try_wait(tfull_bar(0), 0)) j0 = atomicAdd(fp.grid_sync + MM_SYNC_PUSH_HEAD, kPushChunk);
+                if (lane == 0 && !mbar_try_wait(tfull_bar(0), 0)) j0 = atomicAdd(fp.grid_sync + MM_SYNC_PUSH_HEAD, kPushChunkStart);
                 j0 = __shfl_sync(0xffffffffu, j0, 0);
                 if (j0 >= n_send) break;
-                push_chunk(fp, j0, n_send, lane);
+                push_chunk(fp, j0, kPushChunkStart, n_send, lane);
             }
         }
         // Scout: one lane checks, without blocking, whether the dependencies of this CTA's NEXT tiles are met (arrival
@@ -691,10 +695,12 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
             __threadfence_block();
             *reinterpret_cast<volatile int*>(s_misc + 4) = scout_n;
         };
+        int pending_mb = -1, local_i = -1;
         for (int tile = blockIdx.x; tile < tiles_all && alive; tile += gridDim.x) {
             if (*abort_flag != 0) break;
             int kind, mb, nb;
             order.seek(tile, kind, mb, nb);
+            ++local_i;
             const bool second = kind == WaveOrder::kG2;
             const GemmParams& g = second ? g2 : g1;
             const int e = g.mblock_expert[mb];
@@ -715,18 +721,36 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
             named_bar_sync(1, kEpilogueThreads);
             if (is_scout) scout_step();
             __syncwarp();
+            // Things done here cost nothing while the tensor pipe is the bottleneck (the accumulator is not complete yet):
+            // count the previous GEMM1 tile's share towards its m-block (the fence waits for this warp's stores), and, if the
+            // scout has confirmed this tile's dependency, fetch the row's metadata before the accumulator wait instead of after.
+            if (pending_mb >= 0) {
+                if (lane == 0) { __threadfence(); red_release_gpu_add(fp.l1_done + pending_mb, 1); }
+                pending_mb = -1;
+            }
+            const bool early = local_i < *reinterpret_cast<volatile int*>(s_misc + 4);
+            uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+            float a_scale = 0.0f;
+            if (early && row_ok) {
+                __threadfence_block();
+                raw = __ldcg(reinterpret_cast<const uint4*>(g.meta + row));
+                if (second) a_scale = __ldcg(g.act_scale + row);
+            }
             if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, g.timeout_ns)) { alive = false; break; }
             tc_fence_after();
             // the accumulator is complete, so the m-block's rows (and, for GEMM2, its activation scales) are in place
             float row_scale = 0.0f, route_w = 0.0f;
             uint8_t* out_ptr = nullptr;
             if (row_ok) {
-                const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(g.meta + row));
+                if (!early) {
+                    raw = __ldcg(reinterpret_cast<const uint4*>(g.meta + row));
+                    if (second) a_scale = __ldcg(g.act_scale + row);
+                }
                 if (!second) {
                     row_scale = __uint_as_float(raw.x);
                     route_w = __uint_as_float(raw.y);
                 } else {
-                    row_scale = __ldcg(g.act_scale + row);
+                    row_scale = a_scale;
                     out_ptr = combine_row_ptr(g, static_cast<int>(raw.w), static_cast<int>(raw.z));
                 }
             }
@@ -737,15 +761,11 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
             if (lane == 0) mbar_arrive(tempty_bar(acc));
             if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
 
-            if (!second) {
-                // this warp's share of the tile (bf16 values, row amax) is stored: count it towards the m-block's GEMM1 total
-                __syncwarp();
-                if (lane == 0) {
-                    __threadfence();
-                    red_release_gpu_add(fp.l1_done + mb, 1);
-                }
-            }
+            // this warp's share of a GEMM1 tile (bf16 values, row amax) is stored: it is counted towards the m-block's total at
+            // the next idle point (above), or right after the loop
+            if (!second) pending_mb = mb;
         }
+        if (pending_mb >= 0 && lane == 0) { __threadfence(); red_release_gpu_add(fp.l1_done + pending_mb, 1); }
     }
 
     __threadfence_system();

@@ -123,7 +123,14 @@ __global__ void __launch_bounds__(256) requant_kernel(const __nv_bfloat16* __res
 // The reference zeroes those slots during its route scan; here they are skipped using the same validity rule.
 __global__ void __launch_bounds__(256, 4) combine_reduce_kernel(const uint8_t* __restrict__ sym, MmSymLayout sl, int E, int T, int K, int H,
                                                             int num_tokens, const int* __restrict__ runtime_num_tokens,
-                                                            __nv_bfloat16* __restrict__ y, const int* __restrict__ status) {
+                                                            __nv_bfloat16* __restrict__ y, const int* __restrict__ status,
+                                                            int* __restrict__ reset_a, int reset_a_words,
+                                                            int* __restrict__ reset_b, int reset_b_words) {
+    // Leave the layer kernel's dependency counters zero for the next call (null pointers: nothing to reset).  reset_b are
+    // the arrival counters in the symmetric buffer: peers bump them again only after this rank has entered its next call
+    // (they wait for its route counts first), which on the stream comes after this kernel.
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < reset_a_words; i += gridDim.x * blockDim.x) reset_a[i] = 0;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < reset_b_words; i += gridDim.x * blockDim.x) reset_b[i] = 0;
     if (status[0] != 0) return;       // a bounded wait expired earlier in the call: y stays untouched
     // a device-side count (graph mode) never exceeds the launch-time count = rows of y
     int n = runtime_num_tokens ? *runtime_num_tokens : num_tokens;

@@ -49,36 +49,14 @@ __device__ __forceinline__ void report_status(uint8_t* scratch, const MmScratchL
     }
 }
 
-// ---- 1. per-block histogram of valid routes ------------------------------------------------------------------
-// grid = route_blocks, block = MM_ROUTE_CHUNK threads; thread i of block b owns route b*CHUNK + i (token-major).
-__global__ void __launch_bounds__(MM_ROUTE_CHUNK) route_count_kernel(RouteParams p) {
-    __shared__ int hist[MM_MAX_EXPERTS];
-    const int n_routes = route_num_tokens(p) * p.K;
-    for (int e = threadIdx.x; e < p.E; e += blockDim.x) hist[e] = 0;
-    __syncthreads();
-    const int route = blockIdx.x * MM_ROUTE_CHUNK + threadIdx.x;
-    if (route < n_routes) {
-        const int64_t e = reinterpret_cast<const int64_t*>(p.sym + p.sl.topk_idx)[route];
-        const float w = reinterpret_cast<const float*>(p.sym + p.sl.topk_weights)[route];
-        if (e >= 0 && e < p.E && w != 0.0f) atomicAdd(&hist[static_cast<int>(e)], 1);
-    }
-    __syncthreads();
-    int* bc = reinterpret_cast<int*>(p.scratch + p.cl.block_counts) + static_cast<int64_t>(blockIdx.x) * p.E;
-    for (int e = threadIdx.x; e < p.E; e += blockDim.x) bc[e] = hist[e];
-    if (blockIdx.x == 0 && threadIdx.x == 0) {
-        int* epoch = reinterpret_cast<int*>(p.scratch + p.cl.epoch);
-        epoch[0] = epoch[0] + 1;   // one epoch per layer call; later kernels of the call read it
-    }
-}
-
-// ---- 2. prefix over blocks, publish this rank's count vector to every rank -------------------------------------
-// grid = 1, block = 1024.
-__global__ void __launch_bounds__(1024) route_exchange_kernel(RouteParams p) {
+// ---- 1. per-block histogram of valid routes; the block that finishes last turns the histograms into prefixes over the
+//         blocks and publishes this rank's count vector to every rank -----------------------------------------------
+// grid = route_blocks, block = 1024 threads; thread i < MM_ROUTE_CHUNK of block b owns route b*CHUNK + i (token-major).
+__device__ __forceinline__ void route_exchange_block(const RouteParams& p, int* part_sum) {
     const int route_blocks = static_cast<int>(p.cl.route_blocks);
     int* bc = reinterpret_cast<int*>(p.scratch + p.cl.block_counts);
     // blockDim / E threads share one expert: each sums a contiguous range of blocks, then turns its range into an
     // exclusive prefix starting from the ranges before it (loads are independent, so they overlap)
-    __shared__ int part_sum[1024];
     const int parts = max(1, min(static_cast<int>(blockDim.x) / p.E, 32));
     const int per = (route_blocks + parts - 1) / parts;
     for (int e0 = 0; e0 < p.E; e0 += blockDim.x / parts) {
@@ -89,7 +67,7 @@ __global__ void __launch_bounds__(1024) route_exchange_kernel(RouteParams p) {
         int sum = 0;
         if (on) {
 #pragma unroll 8
-            for (int b = b0; b < b1; ++b) sum += bc[static_cast<int64_t>(b) * p.E + e];
+            for (int b = b0; b < b1; ++b) sum += __ldcg(bc + static_cast<int64_t>(b) * p.E + e);
         }
         part_sum[threadIdx.x] = sum;
         __syncthreads();
@@ -99,7 +77,7 @@ __global__ void __launch_bounds__(1024) route_exchange_kernel(RouteParams p) {
             int vals[8];
             for (int b = b0; b < b1; b += 8) {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) vals[i] = (b + i < b1) ? bc[static_cast<int64_t>(b + i) * p.E + e] : 0;
+                for (int i = 0; i < 8; ++i) vals[i] = (b + i < b1) ? __ldcg(bc + static_cast<int64_t>(b + i) * p.E + e) : 0;
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     if (b + i < b1) bc[static_cast<int64_t>(b + i) * p.E + e] = run;   // rows of earlier blocks
@@ -124,6 +102,38 @@ __global__ void __launch_bounds__(1024) route_exchange_kernel(RouteParams p) {
             st_release_sys(sig + MM_BAR_COUNTS * MM_MAX_RANKS + p.rank, epoch);
         }
     }
+}
+
+__global__ void __launch_bounds__(1024) route_count_kernel(RouteParams p) {
+    __shared__ int hist[MM_MAX_EXPERTS];           // later reused as the partial sums of the exchange step
+    __shared__ int s_last;
+    const int n_routes = route_num_tokens(p) * p.K;
+    for (int e = threadIdx.x; e < p.E; e += blockDim.x) hist[e] = 0;
+    __syncthreads();
+    const int route = blockIdx.x * MM_ROUTE_CHUNK + threadIdx.x;
+    if (threadIdx.x < MM_ROUTE_CHUNK && route < n_routes) {
+        const int64_t e = reinterpret_cast<const int64_t*>(p.sym + p.sl.topk_idx)[route];
+        const float w = reinterpret_cast<const float*>(p.sym + p.sl.topk_weights)[route];
+        if (e >= 0 && e < p.E && w != 0.0f) atomicAdd(&hist[static_cast<int>(e)], 1);
+    }
+    __syncthreads();
+    int* bc = reinterpret_cast<int*>(p.scratch + p.cl.block_counts) + static_cast<int64_t>(blockIdx.x) * p.E;
+    for (int e = threadIdx.x; e < p.E; e += blockDim.x) bc[e] = hist[e];
+    // the last block to get here has every block's histogram in front of it
+    int* epoch = reinterpret_cast<int*>(p.scratch + p.cl.epoch);
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int done = atomicAdd(epoch + 1, 1) + 1;
+        s_last = done == static_cast<int>(gridDim.x) ? 1 : 0;
+        if (s_last) {
+            epoch[1] = 0;                          // ready for the next call
+            epoch[0] = epoch[0] + 1;               // one epoch per layer call; later kernels of the call read it
+            __threadfence();
+        }
+    }
+    __syncthreads();
+    if (s_last) route_exchange_block(p, hist);
 }
 
 // Bounded wait until every rank has published `epoch` on barrier `bar` of the LOCAL signal block.

@@ -100,6 +100,7 @@ def run_cuda_rank(case: Case, rank: int, group=None, clamp=None, t_max: Optional
     if variant is not None:
         sb._large_opt_3stage_mode = {"fused": "off", "staged": "force", "split": "force"}[variant]
         sb._staged_split = variant == "split"
+        sb._staged_split_auto = False
     if quantise_on_device:
         w1 = megamoe.transform_fp8_weights_for_mega_moe(case.w1_bf16[rank].to(dev), case.w2_bf16[rank].to(dev),
                                                         layout="marlin" if marlin else "tiled")

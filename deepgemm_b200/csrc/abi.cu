@@ -30,6 +30,9 @@ thread_local char g_err[512] = "";
 std::atomic<int64_t> g_launches{0};
 std::atomic<int> g_barrier_ms{30000};
 std::atomic<int> g_pipe_ms{4000};
+// tuning switches of the layer kernel (FusedParams::policy, waves of its tile order): environment at load, or mm_set_tuning
+std::atomic<int> g_policy{[] { const char* v = getenv("MEGAMOE_HELPER_POLICY"); return v ? atoi(v) : 2; }()};
+std::atomic<int> g_wave_mblocks{[] { const char* v = getenv("MEGAMOE_WAVE_MBLOCKS"); return v ? atoi(v) : 0; }()};
 
 int fail(int code, const char* fmt, ...) {
     va_list ap;
@@ -566,10 +569,9 @@ int mm_fp8_w8a8_mega_moe(void* y, const void* w1, const float* s1, const void* w
     // a wave holds enough GEMM1 tiles for about two rounds over the SMs; its GEMM2 tiles come up kWaveLookahead waves later,
     // by when its requantisation is done
     fp.wave_mblocks = (2 * sms + g1.n_blocks - 1) / g1.n_blocks;
-    static const int wave_override = [] { const char* v = getenv("MEGAMOE_WAVE_MBLOCKS"); return v ? atoi(v) : 0; }();   // tuning aid
+    const int wave_override = g_wave_mblocks.load();                      // tuning aid (MEGAMOE_WAVE_MBLOCKS / mm_set_tuning)
     if (wave_override != 0) fp.wave_mblocks = wave_override > 0 ? wave_override : (1 << 28);
-    static const int helper_policy = [] { const char* v = getenv("MEGAMOE_HELPER_POLICY"); return v ? atoi(v) : 2; }();   // tuning aid
-    fp.policy = helper_policy;
+    fp.policy = g_policy.load();                                          // tuning aid (MEGAMOE_HELPER_POLICY / mm_set_tuning)
     void* fused_args[] = {&tm_pool, &tm_w1, &tm_act, &tm_w2, &fp};
 
     if (mode == MM_MODE_FUSED) {
@@ -645,12 +647,8 @@ int mm_fp8_w8a8_mega_moe(void* y, const void* w1, const float* s1, const void* w
     else mm::grouped_gemm_kernel<1><<<sms, mm::kGemmThreads, mm::kGemmSmemBytes, stream>>>(tm_act, tm_w2, g2);
     MM_STAGE(MM_STAGE_GEMM2);
     }   // split launches
-    if (R > 1) {
-        mm::rank_barrier_kernel<<<1, 32, 0, stream>>>(rp, MM_BAR_COMBINE);
-        MM_STAGE(MM_STAGE_BARRIER_COMBINE);
-    }
-    mm::combine_reduce_kernel<<<sms * 8, 256, 0, stream>>>(rp.sym, rp.sl, E, T_max, K, H, num_tokens, runtime_num_tokens,
-                                                          static_cast<__nv_bfloat16*>(y), g1.status, reset_a, reset_a_words,
+    // the reduce kernel does the cross-rank "combine stores done" barrier itself before it reads the combine buffer
+    mm::combine_reduce_kernel<<<sms * 8, 256, 0, stream>>>(rp, static_cast<__nv_bfloat16*>(y), R > 1 ? 1 : 0, reset_a, reset_a_words,
                                                           reset_b, reset_b_words);
     MM_STAGE(MM_STAGE_REDUCE);
 #undef MM_STAGE
@@ -669,6 +667,13 @@ int mm_set_timeouts(int rank_barrier_ms, int pipeline_ms) {
     MM_REQUIRE(rank_barrier_ms > 0 && pipeline_ms > 0, "timeouts must be positive");
     g_barrier_ms.store(rank_barrier_ms);
     g_pipe_ms.store(pipeline_ms);
+    return 0;
+}
+
+int mm_set_tuning(int policy, int wave_mblocks) {
+    MM_REQUIRE(policy >= 0, "mm_set_tuning: policy must be non-negative");
+    g_policy.store(policy);
+    g_wave_mblocks.store(wave_mblocks);
     return 0;
 }
 

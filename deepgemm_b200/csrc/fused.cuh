@@ -23,8 +23,9 @@
 //     rows are still crossing NVLink.  The combine barrier, the reduce and the counter reset are launches after it.
 //
 // Step 4, the tile loop: m-blocks are grouped in waves; with G1(k) / G2(k) = all GEMM1 / GEMM2 tiles of wave k the
-// order is  G1(0), G1(1), G1(2), [G1(3), G2(0)], [G1(4), G2(1)], ..., G2(n-1)  (round-robin over CTAs), so the tensor-bound
-// GEMM1 work overlaps the NVLink-bound combine stores of GEMM2.  Dependencies are per m-block, never global barriers:
+// order is  G1(0), G1(1), G1(2), {G1(3), G2(0)}, {G1(4), G2(1)}, ..., G2(n-1), the two lists of a {group} alternating tile
+// by tile, and CTAs take tiles from this order dynamically: tensor-bound GEMM1 work overlaps the NVLink-bound combine
+// stores of GEMM2 on every SM all the time.  Dependencies are per m-block, never global barriers:
 //   - GEMM1 tile: weights start streaming at once; the token operand waits for arrive[m-block] == valid rows; each
 //     epilogue warp counts its stored share in l1_done[m-block];
 //   - requantisation unit (a 32-row quarter of an m-block, claimed in order by the helper warps of ALL CTAs): waits for
@@ -51,7 +52,7 @@ static_assert(kFusedFirstEpilogueWarp % 4 == 0, "epilogue warps must start at a 
 // words of the `plan` array in the scratch buffer (written by route_plan_kernel or by this kernel's step 2)
 enum { MM_PLAN_MBLOCKS = 0, MM_PLAN_ROWS_PADDED = 1, MM_PLAN_PAIRS = 2, MM_PLAN_SEND = 3, MM_PLAN_ROWS_EXPECTED = 6 };
 // words of the `grid_sync` array: all zero between calls (this kernel's last step, or a memset after a gemm_only launch)
-enum { MM_SYNC_CTAS = 0, MM_SYNC_CALLS = 1, MM_SYNC_UNITS_DONE = 2, MM_SYNC_PUSH_HEAD = 3, MM_SYNC_REQUANT_HEAD = 4 };
+enum { MM_SYNC_CTAS = 0, MM_SYNC_CALLS = 1, MM_SYNC_UNITS_DONE = 2, MM_SYNC_PUSH_HEAD = 3, MM_SYNC_REQUANT_HEAD = 4, MM_SYNC_TILE_HEAD = 5 };
 
 struct FusedParams {
     RouteParams rp;
@@ -66,7 +67,7 @@ struct FusedParams {
     float* act_scale_w;    // writable alias of g2.act_scale
     int wave_mblocks;      // m-blocks per wave of the tile order
     int gemm_only;         // 1: routing was done by the staged kernels; start at the tile loop and stop after it
-    int policy;            // tuning switches: bit 0 = both helper warps push even with several ranks,
+    int policy;            // tuning switches: bit 0 = both helper warps push (default: one pushes, one requantises from the start),
                            //                  bit 1 = epilogue warps help pushing until their first accumulator is complete
 };
 
@@ -98,37 +99,70 @@ __device__ __forceinline__ bool wait_flag_ge(const int* flag, int target, bool s
     }
 }
 
-// Position of a tile index in the wave order.  A CTA's tile indices grow, so seek() only moves forward.
-// Groups: G1(0) .. G1(L-1), then pairs G1(k+L), G2(k) with L = kWaveLookahead: a wave's requantisation has L waves of
-// GEMM1 tiles (about 2 L rounds over the SMs) to finish before its GEMM2 tiles come up.
+// Position of a tile index in the tile order.  A CTA's tile indices grow, so seek() only moves forward.
+// Groups: G1(0) .. G1(L-1) alone, then for k = 0, 1, ... the group {G1(k+L), G2(k)} whose tiles ALTERNATE one by one (the
+// longer list's surplus follows), L = kWaveLookahead: a wave's requantisation has L waves of GEMM1 tiles to finish before
+// its GEMM2 tiles come up, and at any moment the SMs are a steady mix of tensor-bound GEMM1 tiles and GEMM2 tiles whose
+// epilogues write over NVLink -- instead of all SMs bursting onto the link at once.
 constexpr int kWaveLookahead = 3;
 struct WaveOrder {
     enum { kG1 = 0, kG2 = 1 };
     int n_waves, wave_m, num_mblocks, nb1, nb2;
-    int g, base, size, kind, wave;
-    __device__ WaveOrder(int num_mblocks_, int wave_m_, int nb1_, int nb2_)
+    int g, base, size, n1, n2, w1, w2;          // current group: n1 GEMM1 tiles of wave w1, n2 GEMM2 tiles of wave w2
+    bool tile_interleave;                       // false: inside a group all GEMM1 tiles come before the GEMM2 tiles
+    __device__ WaveOrder(int num_mblocks_, int wave_m_, int nb1_, int nb2_, bool tile_interleave_)
         : n_waves((num_mblocks_ + wave_m_ - 1) / wave_m_), wave_m(wave_m_), num_mblocks(num_mblocks_), nb1(nb1_), nb2(nb2_),
-          g(0), base(0) { set(); }
+          g(0), base(0), tile_interleave(tile_interleave_) { set(); }
     __device__ __forceinline__ int wave_mblocks(int w) const { return w < n_waves ? min(wave_m, num_mblocks - w * wave_m) : 0; }
     __device__ __forceinline__ void set() {
-        if (g < kWaveLookahead) { kind = kG1; wave = g; }
-        else {
-            const int k = (g - kWaveLookahead) >> 1, j = (g - kWaveLookahead) & 1;
-            kind = j == 0 ? kG1 : kG2;
-            wave = j == 0 ? k + kWaveLookahead : k;
-        }
-        size = wave_mblocks(wave) * (kind == kG1 ? nb1 : nb2);
+        w1 = g;
+        w2 = g - kWaveLookahead;
+        n1 = wave_mblocks(w1) * nb1;
+        n2 = w2 >= 0 ? wave_mblocks(w2) * nb2 : 0;
+        size = n1 + n2;
     }
     // tile -> (kind, m-block, n-block); the caller guarantees tile < num_mblocks * (nb1 + nb2)
     __device__ __forceinline__ void seek(int tile, int& kind_out, int& mb, int& nb) {
         while (tile >= base + size) { base += size; ++g; set(); }
         const int r = tile - base;
-        const int per = kind == kG1 ? nb1 : nb2;
-        mb = wave * wave_m + r / per;
-        nb = r - (r / per) * per;
-        kind_out = kind;
+        const int m = tile_interleave ? min(n1, n2) : 0;
+        int idx;
+        if (r < 2 * m) { kind_out = (r & 1) ? kG2 : kG1; idx = r >> 1; }
+        else if (tile_interleave) { kind_out = n1 > n2 ? kG1 : kG2; idx = r - m; }
+        else { kind_out = r < n1 ? kG1 : kG2; idx = r < n1 ? r : r - n1; }
+        const int per = kind_out == kG1 ? nb1 : nb2;
+        mb = (kind_out == kG1 ? w1 : w2) * wave_m + idx / per;
+        nb = idx - (idx / per) * per;
     }
 };
+
+// Tiles are handed out dynamically: the producer thread of a CTA claims the next tile index from a global counter (one
+// claim ahead, so the atomic's latency is hidden), and publishes it to the CTA's other roles through a small ring in shared
+// memory: slot j % 8 holds {j, tile} for the CTA's j-th tile, tile < 0 = no more tiles.  The producer is never more than
+// three tiles ahead of the epilogue (two accumulators, four operand stages), so eight slots cannot wrap onto a live one.
+constexpr int kTileRing = 8;
+__device__ __forceinline__ void ring_publish(volatile int* ring, int j, int tile) {
+    ring[2 * (j & (kTileRing - 1)) + 1] = tile;
+    __threadfence_block();
+    ring[2 * (j & (kTileRing - 1))] = j;
+}
+// the j-th tile of this CTA once the producer has published it; kRingAbort when the CTA gave up or the wait ran out
+constexpr int kRingAbort = -2;
+__device__ __forceinline__ int ring_wait(const volatile int* ring, int j, volatile int* abort_flag, uint64_t timeout_ns) {
+    const volatile int* slot = ring + 2 * (j & (kTileRing - 1));
+    if (slot[0] != j) {
+        const uint64_t t0 = global_timer_ns();
+        uint32_t it = 0;
+        while (slot[0] != j) {
+            if ((++it & 63u) == 0u) {
+                if (*abort_flag != 0) return kRingAbort;
+                if (global_timer_ns() - t0 > timeout_ns) { *abort_flag = 1; return kRingAbort; }
+            }
+        }
+    }
+    __threadfence_block();
+    return slot[1];
+}
 
 // Copy up to two FP8 rows of `H` bytes (16-byte vectors, all their loads in flight together) -- the data part of a push.
 __device__ __forceinline__ void push_two_rows(const uint8_t* src0, uint8_t* dst0, const uint8_t* src1, uint8_t* dst1, int H, int lane) {
@@ -279,6 +313,7 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail + 8);
     int* s_misc = reinterpret_cast<int*>(tail + 16);       // [0] number of m-blocks, [1] ok flag of block-wide waits, [2] rows to receive,
                                                            // [4] leading tiles of this CTA whose dependency the scout has confirmed
+    volatile int* tile_ring = reinterpret_cast<volatile int*>(tail + 48);   // kTileRing x {sequence number, tile}
     FusedRouteSmem& rs = *reinterpret_cast<FusedRouteSmem*>(smem_gen);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -295,6 +330,7 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
         for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), kEpilogueWarps); }
         *abort_flag = 0;
         s_misc[0] = 0; s_misc[1] = ld_acquire_gpu(status) == 0 ? 1 : 0; s_misc[2] = 0; s_misc[4] = 0;
+        for (int i = 0; i < kTileRing; ++i) tile_ring[2 * i] = -1;
         fence_barrier_init();
         prefetch_tensormap(&tm_pool); prefetch_tensormap(&tm_w1); prefetch_tensormap(&tm_act); prefetch_tensormap(&tm_w2);
     }
@@ -495,7 +531,7 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
     const GemmParams& g1 = fp.g1;
     const GemmParams& g2 = fp.g2;
     const int nb1 = g1.n_blocks, nb2 = g2.n_blocks;
-    const WaveOrder order_init(num_mblocks, max(1, fp.wave_mblocks), nb1, nb2);
+    const WaveOrder order_init(num_mblocks, max(1, fp.wave_mblocks), nb1, nb2, (fp.policy & 4) == 0);
     const int tiles_all = healthy ? num_mblocks * (nb1 + nb2) : 0;
     const int requant_units = healthy ? num_mblocks * 4 : 0;
     const int* arrive = reinterpret_cast<const int*>(rp.sym + rp.sl.pool_arrive);
@@ -510,10 +546,16 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
         WaveOrder order = order_init;
         int local_i = -1;                                   // index of the tile in this CTA's sequence
         uint64_t polled_g1 = 0, polled_g2 = 0;              // time this thread itself spent polling for GEMM1 / GEMM2 tiles (tuning aid)
-        for (int tile = blockIdx.x; tile < tiles_all && alive; tile += gridDim.x) {
+        int* tile_head = fp.grid_sync + MM_SYNC_TILE_HEAD;
+        const bool static_tiles = (fp.policy & 8) != 0;      // measurement aid: round-robin assignment instead of claiming
+        int tile = tiles_all > 0 ? (static_tiles ? static_cast<int>(blockIdx.x) : atomicAdd(tile_head, 1)) : tiles_all;
+        for (; tile < tiles_all && alive;) {
+            // claimed one ahead: needed only when this tile's loads are issued
+            const int next_tile = static_tiles ? tile + static_cast<int>(gridDim.x) : atomicAdd(tile_head, 1);
+            ++local_i;
+            ring_publish(tile_ring, local_i, tile);
             int kind, mb, nb;
             order.seek(tile, kind, mb, nb);
-            ++local_i;
             const bool second = kind == WaveOrder::kG2;
             const GemmParams& g = second ? g2 : g1;
             const int e = g.mblock_expert[mb];
@@ -560,7 +602,9 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
                 if (++stage == kStages) { stage = 0; phase ^= 1u; }
                 if (!alive) break;
             }
+            tile = next_tile;
         }
+        ring_publish(tile_ring, local_i + 1, -1);                // no more tiles for this CTA
         stamp(7);
         if (blockIdx.x == 0) { status[14] = static_cast<int>(polled_g1 / 100); status[15] = static_cast<int>(polled_g2 / 100); }
         }
@@ -573,7 +617,9 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
         int acc = 0; uint32_t acc_phase = 0;
         bool alive = true;
         WaveOrder order = order_init;
-        for (int tile = blockIdx.x; tile < tiles_all && alive; tile += gridDim.x) {
+        for (int j = 0; alive; ++j) {
+            const int tile = ring_wait(tile_ring, j, abort_flag, rp.barrier_timeout_ns);
+            if (tile < 0) break;
             int kind, mb, nb;
             order.seek(tile, kind, mb, nb);
             const GemmParams& g = kind == WaveOrder::kG2 ? g2 : g1;
@@ -614,9 +660,9 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
         const int l1_target = nb1 * kEpilogueWarps;
 
         int* requant_head = fp.grid_sync + MM_SYNC_REQUANT_HEAD;
-        // (a) push: walk the send list until it is exhausted (policy bit 0 clear: only warp 2 of a CTA pushes once several
-        //     ranks are involved, so that warp 3 requantises from the start and GEMM2 tiles never wait for the link)
-        const bool pusher = (fp.policy & 1) != 0 || rp.R == 1 || warp == 2;
+        // (a) push: walk the send list until it is exhausted.  Only warp 2 of a CTA pushes (policy bit 0: both do), so that
+        //     warp 3 requantises from the start and GEMM2 tiles never wait for the push to finish.
+        const bool pusher = (fp.policy & 1) != 0 || warp == 2;
         for (int it = 0; pusher; ++it) {
             const int chunk = it < 2 ? kPushChunkStart : kPushChunk;
             int j0 = 0;
@@ -674,33 +720,39 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
         // global-memory round trip in front of every tile.  Counters only grow during a call: a confirmation stays valid.
         const bool is_scout = warp == kFusedFirstEpilogueWarp && lane == 0;
         WaveOrder scout_order = order_init;
-        int scout_tile = blockIdx.x, scout_n = 0, scout_polls = 0;
+        int scout_n = 0, scout_polls = 0;                    // tiles of this CTA confirmed so far (in ring order)
         bool scout_all_arrived = false, scout_all_ready = false;
-        auto scout_step = [&]() {
-            for (int n = 0; n < 2 && scout_tile < tiles_all; ++n) {
+        auto scout_step = [&](int j_epilogue) {
+            if (scout_n < j_epilogue) scout_n = j_epilogue;   // tiles the epilogue has reached were loaded: nothing left to confirm
+            for (int n = 0; n < 2; ++n) {
+                const volatile int* slot = tile_ring + 2 * (scout_n & (kTileRing - 1));
+                if (slot[0] != scout_n) break;                // not published yet
+                __threadfence_block();
+                const int t = slot[1];
+                if (t < 0) break;
                 int kind, mb, nb;
-                scout_order.seek(scout_tile, kind, mb, nb);
+                scout_order.seek(t, kind, mb, nb);
                 bool ok;
                 if (kind == WaveOrder::kG2) {
-                    if (!scout_all_ready && (scout_polls++ & 7) == 0) scout_all_ready = ld_acquire_gpu(fp.grid_sync + 2) - requant_units >= 0;
+                    if (!scout_all_ready && (scout_polls++ & 7) == 0) scout_all_ready = ld_acquire_gpu(fp.grid_sync + MM_SYNC_UNITS_DONE) - requant_units >= 0;
                     ok = scout_all_ready || ld_acquire_gpu(fp.l2_ready + mb) - 4 >= 0;
                 } else {
                     if (!scout_all_arrived && (scout_polls++ & 7) == 0) scout_all_arrived = ld_acquire_sys(arrive + arrive_total_slot) - rows_expected >= 0;
                     ok = scout_all_arrived || ld_acquire_sys(arrive + mb) - g1.mblock_valid[mb] >= 0;
                 }
                 if (!ok) break;
-                scout_tile += gridDim.x;
                 ++scout_n;
             }
             __threadfence_block();
             *reinterpret_cast<volatile int*>(s_misc + 4) = scout_n;
         };
-        int pending_mb = -1, local_i = -1;
-        for (int tile = blockIdx.x; tile < tiles_all && alive; tile += gridDim.x) {
+        int pending_mb = -1;
+        for (int local_i = 0; alive; ++local_i) {
             if (*abort_flag != 0) break;
+            const int tile = ring_wait(tile_ring, local_i, abort_flag, rp.barrier_timeout_ns);
+            if (tile < 0) break;
             int kind, mb, nb;
             order.seek(tile, kind, mb, nb);
-            ++local_i;
             const bool second = kind == WaveOrder::kG2;
             const GemmParams& g = second ? g2 : g1;
             const int e = g.mblock_expert[mb];
@@ -719,7 +771,7 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
                 }
             }
             named_bar_sync(1, kEpilogueThreads);
-            if (is_scout) scout_step();
+            if (is_scout) scout_step(local_i);
             __syncwarp();
             // Things done here cost nothing while the tensor pipe is the bottleneck (the accumulator is not complete yet):
             // count the previous GEMM1 tile's share towards its m-block (the fence waits for this warp's stores), and, if the
@@ -820,7 +872,7 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
                         const int64_t e = topk_idx[static_cast<int64_t>(t) * rp.K + s];
                         const float w = topk_w[static_cast<int64_t>(t) * rp.K + s];
                         ok[j] = e >= 0 && e < rp.E && w != 0.0f;
-                        if (ok[j]) buf[j] = __ldcg(comb + (static_cast<int64_t>(s) * rp.T + t) * vecs + v);
+                        if (ok[j]) buf[j] = __ldcg(comb + (static_cast<int64_t>(t) * rp.K + s) * vecs + v);
                     }
                 }
 #pragma unroll
@@ -847,6 +899,7 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
             fp.grid_sync[2] = 0;
             fp.grid_sync[MM_SYNC_REQUANT_HEAD] = 0;
             fp.grid_sync[MM_SYNC_PUSH_HEAD] = 0;
+            fp.grid_sync[MM_SYNC_TILE_HEAD] = 0;
             reinterpret_cast<int*>(rp.scratch + rp.cl.epoch)[0] = epoch;
             fp.grid_sync[1] = fused_calls + 1;
         }

@@ -3,7 +3,7 @@
 //   kind 0 (GEMM1): act[row, j] = bf16( silu(g) * u * w_route ),  g = acc_gate * (sx[row] * s1[j]),  u likewise with
 //                   weight row I + j; also the per-row amax of the bf16 values.  Replaces
 //                   deep_gemm/include/deep_gemm/impls/mega_moe_dcu_tiles.cuh:380-670 (compute_route_mmac_mtile16_l1_chunk).
-//   kind 1 (GEMM2): out[row, h] = bf16( acc * (s2[row] * sw2[h]) ) stored straight into combine[slot][token][:] of the
+//   kind 1 (GEMM2): out[row, h] = bf16( acc * (s2[row] * sw2[h]) ) stored straight into combine[token][slot][:] of the
 //                   SOURCE rank over NVLink.  Replaces impls/mega_moe_dcu_tiles.cuh:735-1163.
 //
 // One persistent CTA per SM, 320 threads: warp 0 = TMA producer, warp 1 = MMA issuer (owns TMEM), warps 2-9 = epilogue.
@@ -62,14 +62,14 @@ struct GemmParams {
     uint64_t timeout_ns;
 };
 
-// Destination of one GEMM2 output row: combine[slot][token][:] on the SOURCE rank.  The row's metadata was written by
+// Destination of one GEMM2 output row: combine[token][slot][:] on the SOURCE rank.  The row's metadata was written by
 // that rank; a pool row nobody wrote in this call (error path, stale or uninitialised memory) may name anything, so the
 // three indices are range-checked and a row that fails the check is not stored at all.
 __device__ __forceinline__ uint8_t* combine_row_ptr(const GemmParams& p, int src_info, int src_token) {
     const int src_rank = src_info >> 8, slot = src_info & 0xff;
     if (src_rank < 0 || src_rank >= p.R || slot >= p.K || src_token < 0 || src_token >= p.T) return nullptr;
     return reinterpret_cast<uint8_t*>(p.peers[src_rank]) + p.combine_off +
-           (static_cast<int64_t>(slot) * p.T + src_token) * p.H * 2;
+           (static_cast<int64_t>(src_token) * p.K + slot) * p.H * 2;
 }
 
 // x * sigmoid(x) with the fast exponential and reciprocal units, as the reference does

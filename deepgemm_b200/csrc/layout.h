@@ -54,7 +54,8 @@ struct MmSymLayout {
     int64_t topk_weights;       // f32    [T][K]
     int64_t pool_x;             // fp8    [pool_rows][H]   written by source ranks
     int64_t pool_meta;          // MmPoolMeta [pool_rows]
-    int64_t combine;            // bf16   [K][T][H]        written by owner ranks
+    int64_t combine;            // bf16   [T][K][H]        written by owner ranks; a token's K slots are adjacent, so the rows of one
+                                //                         GEMM2 tile (consecutive tokens of one source rank) land in a few MiB of the peer
     int64_t total;
     int64_t pool_rows;          // capacity in rows (multiple of MM_BLOCK_M)
 };

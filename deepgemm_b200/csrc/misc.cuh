@@ -4,6 +4,7 @@
 #include <cuda_fp8.h>
 #include "layout.h"
 #include "ptx.cuh"
+#include "route.cuh"
 
 namespace mm {
 
@@ -119,11 +120,13 @@ __global__ void __launch_bounds__(256) requant_kernel(const __nv_bfloat16* __res
 }
 
 // Top-k combine (deep_gemm/include/deep_gemm/impls/mega_moe_dcu.cuh:706-760):
-//   y[t, :] = bf16( sum_{s=0..K-1} f32(combine[s][t][:]) ) in slot order; slots of invalid routes contribute zero.
+//   y[t, :] = bf16( sum_{s=0..K-1} f32(combine[t][s][:]) ) in slot order; slots of invalid routes contribute zero.
 // The reference zeroes those slots during its route scan; here they are skipped using the same validity rule.
-__global__ void __launch_bounds__(256, 4) combine_reduce_kernel(const uint8_t* __restrict__ sym, MmSymLayout sl, int E, int T, int K, int H,
-                                                            int num_tokens, const int* __restrict__ runtime_num_tokens,
-                                                            __nv_bfloat16* __restrict__ y, const int* __restrict__ status,
+// With several ranks the kernel first does the cross-rank "combine stores done" barrier itself (wait_peers != 0): block 0
+// publishes this rank's call epoch to every rank -- the GEMM2 tiles ran in earlier launches of this stream, so their
+// remote stores are complete -- and every block waits (bounded) until all ranks have published theirs.  A block only ever
+// waits for OTHER ranks' first blocks, never for a block of its own grid.
+__global__ void __launch_bounds__(256, 4) combine_reduce_kernel(RouteParams p, __nv_bfloat16* __restrict__ y, int wait_peers,
                                                             int* __restrict__ reset_a, int reset_a_words,
                                                             int* __restrict__ reset_b, int reset_b_words) {
     // Leave the layer kernel's dependency counters zero for the next call (null pointers: nothing to reset).  reset_b are
@@ -131,15 +134,25 @@ __global__ void __launch_bounds__(256, 4) combine_reduce_kernel(const uint8_t* _
     // (they wait for its route counts first), which on the stream comes after this kernel.
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < reset_a_words; i += gridDim.x * blockDim.x) reset_a[i] = 0;
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < reset_b_words; i += gridDim.x * blockDim.x) reset_b[i] = 0;
-    if (status[0] != 0) return;       // a bounded wait expired earlier in the call: y stays untouched
-    // a device-side count (graph mode) never exceeds the launch-time count = rows of y
-    int n = runtime_num_tokens ? *runtime_num_tokens : num_tokens;
-    n = min(max(n, 0), min(num_tokens, T));
+    if (call_failed(p.scratch, p.cl)) return;       // a bounded wait expired earlier in the call: y stays untouched, peers time out
+    if (wait_peers && p.R > 1) {
+        const int epoch = reinterpret_cast<const int*>(p.scratch + p.cl.epoch)[0];
+        if (blockIdx.x == 0 && threadIdx.x < p.R) {
+            __threadfence_system();
+            int* sig = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(p.peers[threadIdx.x]) + p.sl.signals);
+            st_release_sys(sig + MM_BAR_COMBINE * MM_MAX_RANKS + p.rank, epoch);
+        }
+        const bool ok = wait_rank_signals(p, MM_BAR_COMBINE, epoch);
+        if (!__syncthreads_and(ok)) return;
+    }
+    const uint8_t* sym = p.sym;
+    const int E = p.E, K = p.K, H = p.H;
+    const int n = route_num_tokens(p);              // a device-side count (graph mode) never exceeds the launch-time count = rows of y
     const int vecs = H / 8;
     const int64_t total = static_cast<int64_t>(n) * vecs;
-    const int64_t* topk_idx = reinterpret_cast<const int64_t*>(sym + sl.topk_idx);
-    const float* topk_w = reinterpret_cast<const float*>(sym + sl.topk_weights);
-    const uint4* comb = reinterpret_cast<const uint4*>(sym + sl.combine);
+    const int64_t* topk_idx = reinterpret_cast<const int64_t*>(sym + p.sl.topk_idx);
+    const float* topk_w = reinterpret_cast<const float*>(sym + p.sl.topk_weights);
+    const uint4* comb = reinterpret_cast<const uint4*>(sym + p.sl.combine);
     for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
          i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
         const int t = static_cast<int>(i / vecs), v = static_cast<int>(i - static_cast<int64_t>(t) * vecs);
@@ -155,7 +168,7 @@ __global__ void __launch_bounds__(256, 4) combine_reduce_kernel(const uint8_t* _
                     const int64_t e = topk_idx[static_cast<int64_t>(t) * K + s];
                     const float w = topk_w[static_cast<int64_t>(t) * K + s];
                     ok[j] = e >= 0 && e < E && w != 0.0f;
-                    if (ok[j]) buf[j] = comb[(static_cast<int64_t>(s) * T + t) * vecs + v];
+                    if (ok[j]) buf[j] = __ldcg(comb + (static_cast<int64_t>(t) * K + s) * vecs + v);
                 }
             }
 #pragma unroll

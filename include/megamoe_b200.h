@@ -109,6 +109,15 @@ int mm_read_status(const void* scratch, void* stream, int32_t* out5);
 /* Set the limits of the device-side bounded waits (milliseconds): cross-rank barriers and in-kernel pipelines. */
 int mm_set_timeouts(int rank_barrier_ms, int pipeline_ms);
 
+/* Tuning switches of the layer kernel, for measurements (no counterpart in the reference, whose tile policy is fixed at
+ * compile time, deep_gemm/include/deep_gemm/impls/mega_moe_dcu.cuh:129-137).  policy bits: 1 = both helper warps of a CTA
+ * push rows (default: one pushes, one requantises from the start), 2 = epilogue warps help pushing until their first
+ * accumulator is complete (default on), 4 = inside a wave pair all GEMM1 tiles come before the GEMM2 tiles (default: they
+ * alternate), 8 = tiles assigned round-robin instead of claimed dynamically.  wave_mblocks: m-blocks per wave of the tile
+ * order, 0 = default (about two rounds of GEMM1 tiles), negative = one wave.  Defaults come from MEGAMOE_HELPER_POLICY and
+ * MEGAMOE_WAVE_MBLOCKS at load time.  All ranks of a group must use the same values. */
+int mm_set_tuning(int policy, int wave_mblocks);
+
 /* JSON description of the build.  Replaces get_mega_moe_hip_build_config, csrc/apis/mega_dcu.hpp:28-39. */
 int mm_build_config(char* json, int capacity);
 

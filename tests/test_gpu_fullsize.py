@@ -68,7 +68,7 @@ def test_dsv4_flash_ep1_4096_tokens():
     assert bool((flat[order][1:][same] > flat[order][:-1][same]).all())
 
     # ---- sampled oracle: every row of four experts, compared per route through the combine buffer
-    comb = sb.symm_view("combine", (K, sb.num_max_tokens_per_rank, H), torch.bfloat16)
+    comb = sb.symm_view("combine", (sb.num_max_tokens_per_rank, K, H), torch.bfloat16)
     xq, xs = sb.x[:T].cpu(), sb.x_sf[:T].cpu()
     idx_c, w_c = idx.cpu(), w.cpu()
     for e in (0, 77, 130, 255):
@@ -82,7 +82,7 @@ def test_dsv4_flash_ep1_4096_tokens():
         s2 = (act.abs().amax(dim=1) / 448.0).clamp(min=1e-4)
         aq = (act * (1.0 / s2).view(-1, 1)).to(torch.float8_e4m3fn).float()
         ref = ((aq * s2.view(-1, 1)) @ w2.t()).to(torch.bfloat16)
-        got = comb[kk.cuda(), tt.cuda()].cpu()
+        got = comb[tt.cuda(), kk.cuda()].cpu()
         mc.assert_end_to_end_close(got, ref, f"routes of expert {e}")
 
     # ---- size-independent properties

@@ -29,6 +29,9 @@ E, K, H, I = 256, 6, 4096, 2048
 METRIC, UNIT = "moe_layer_tokens_per_s", "tokens/s"
 FLOP_PER_ROW = 2 * 3 * H * I                     # 50.33 MFLOP per routed row (GEMM1 33.55 + GEMM2 16.78)
 PARITY_SAMPLES = 4                               # tokens per rank checked against the CPU oracle after the timed region
+# DRAM read + write bytes of one layer-kernel launch per expert processed at 96 rows per expert, from an ncu capture of a
+# 32-expert launch (888 MB); the traffic of a launch grows with the experts it processes.  An estimate, labelled as such.
+LAYER_KERNEL_DRAM_BYTES_PER_EXPERT_96ROWS = 888.0e6 / 32
 
 
 def measured_peaks():
@@ -63,6 +66,7 @@ def parity_block(dist, group, rank, world, dev, sb, l1, l2, y, stats, tokens, n_
     from oracle import moe_oracle as orc
     e_loc = E // world
     T = tokens
+    torch.set_num_threads(max(1, (os.cpu_count() or 1) // world))   # every rank runs its share of the oracle on the same host
 
     def gather(t):
         if dist is None:
@@ -635,8 +639,11 @@ def main():
     hbm_peak, peak_kind = measured_peaks()
     achieved = kernel_bytes / (kernel_ms * 1e-3) / 1e9
     roofline = {"kernel": kernel_name, "bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
-                "frac": achieved / hbm_peak, "peak_kind": f"of {peak_kind}", "traffic": None,
-                "traffic_note": "not captured in this run; ncu summaries of small cases are under profiles/",
+                "frac": achieved / hbm_peak, "peak_kind": f"of {peak_kind}",
+                "traffic": (LAYER_KERNEL_DRAM_BYTES_PER_EXPERT_96ROWS * touched
+                            if (not split and 64 <= rows_recv / max(touched, 1) <= 128) else None),
+                "traffic_note": "estimate: scaled from an ncu capture of a 32-expert launch of the same kernel at 96 rows per "
+                                "expert (traffic grows with the experts processed); not measured in this run",
                 "algorithmic_bytes": kernel_bytes, "ms": kernel_ms}
     # With many rows per expert the same kernel is bound by the tensor pipe instead.  The machine-readable peak file has a
     # bf16 figure only, so the FP8 denominator is the library's own probe of the MMA shape the kernel issues, run with

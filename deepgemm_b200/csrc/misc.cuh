@@ -160,15 +160,17 @@ __global__ void __launch_bounds__(256, 4) combine_reduce_kernel(RouteParams p, _
         for (int s0 = 0; s0 < K; s0 += 6) {             // up to six slots' loads in flight, summed in slot order
             uint4 buf[6];
             bool ok[6];
+            // The slot rows are fetched without waiting for the validity of their routes (a slot nobody wrote holds stale
+            // bytes, which are then simply not added): index, weight and row loads are all in flight together.
 #pragma unroll
             for (int j = 0; j < 6; ++j) {
                 const int s = s0 + j;
                 ok[j] = false;
                 if (s < K) {
+                    buf[j] = __ldcg(comb + (static_cast<int64_t>(t) * K + s) * vecs + v);
                     const int64_t e = topk_idx[static_cast<int64_t>(t) * K + s];
                     const float w = topk_w[static_cast<int64_t>(t) * K + s];
                     ok[j] = e >= 0 && e < E && w != 0.0f;
-                    if (ok[j]) buf[j] = __ldcg(comb + (static_cast<int64_t>(t) * K + s) * vecs + v);
                 }
             }
 #pragma unroll

@@ -376,7 +376,8 @@ def run_sweep(args):
                     "max_rows_per_expert": int(allv[:, 3].max()), "rows_max_rank": int(rows_max),
                     "roof_ms": {"tensor": round(t_tensor, 4), "hbm": round(t_hbm, 4), "nvlink": round(t_nvl, 4)},
                     "frac_of_roofline": round(t_roof / ms, 3),
-                    "variant": "fused" if T <= sb._large_opt_3stage_threshold else "staged"}), flush=True)
+                    "variant": "fused" if T <= sb._large_opt_3stage_threshold else
+                               ("staged-split" if megamoe._staged_as_split_launches(sb, T, e_loc) else "staged")}), flush=True)
     sb.destroy()
     if dist is not None:
         dist.barrier(group)

@@ -566,6 +566,7 @@ int mm_fp8_w8a8_mega_moe(void* y, const void* w1, const float* s1, const void* w
     fp.send_list = reinterpret_cast<const int4*>(sc + rp.cl.send_list);
     fp.act_fp8 = sc + rp.cl.act_fp8;
     fp.act_scale_w = reinterpret_cast<float*>(sc + rp.cl.act_scale);
+    fp.w1_tiled = static_cast<const uint8_t*>(w1);
     // a wave holds enough GEMM1 tiles for about two rounds over the SMs; its GEMM2 tiles come up kWaveLookahead waves later,
     // by when its requantisation is done
     fp.wave_mblocks = (2 * sms + g1.n_blocks - 1) / g1.n_blocks;

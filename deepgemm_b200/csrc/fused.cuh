@@ -28,7 +28,7 @@
 // stores of GEMM2 on every SM all the time.  Dependencies are per m-block, never global barriers:
 //   - GEMM1 tile: weights start streaming at once; the token operand waits for arrive[m-block] == valid rows; each
 //     epilogue warp counts its stored share in l1_done[m-block];
-//   - requantisation unit (a 32-row quarter of an m-block, claimed in order by the helper warps of ALL CTAs): waits for
+//   - requantisation unit (a quarter of an m-block's rows, claimed in order by the helper warps of ALL CTAs): waits for
 //     every GEMM1 tile of the m-block (the channelwise scale needs the whole row), converts bf16 -> e4m3, bumps l2_ready;
 //   - GEMM2 tile: the activation operand waits for l2_ready[m-block] == 4.
 // A tile only ever waits for work that belongs to tiles earlier in the order (or for pushes, which wait for nothing),
@@ -65,6 +65,7 @@ struct FusedParams {
     const int4* send_list; // [valid routes] {route, pool row, owner rank, token} in send order (gemm_only)
     uint8_t* act_fp8;      // [pool_rows][I]
     float* act_scale_w;    // writable alias of g2.act_scale
+    const uint8_t* w1_tiled;   // GEMM1 weights as stored (the tensor map's base): L2 prefetch while the routing steps run
     int wave_mblocks;      // m-blocks per wave of the tile order
     int gemm_only;         // 1: routing was done by the staged kernels; start at the tile loop and stop after it
     int policy;            // tuning switches: bit 0 = both helper warps push (default: one pushes, one requantises from the start),
@@ -236,15 +237,17 @@ __device__ __forceinline__ void push_chunk(const FusedParams& fp, int j0, int ch
     }
 }
 
-// One requantisation unit (helper warps): rows [32q, 32q+32) of m-block mb, bf16 -> e4m3 with one scale per row,
+// One requantisation unit (helper warps): a quarter of the row pairs of m-block mb, bf16 -> e4m3 with one scale per row,
 // s2 = max(amax / 448, 1e-4) (deep_gemm/include/deep_gemm/impls/mega_moe_dcu_tiles.cuh:672-733), then count the quarter
 // towards l2_ready[mb].  The caller has seen, with an acquire load, that every GEMM1 tile of the m-block is stored.
 __device__ __forceinline__ void requant_unit(const FusedParams& fp, int u, int lane) {
     const GemmParams& g1 = fp.g1;
     const int inter = g1.n_out, vecs = inter / 8;
-    const int mb = u >> 2, r_lo = (u & 3) * 32;
-    const int r_hi = min(r_lo + 32, g1.mblock_valid[mb]);
-    for (int r = r_lo; r < r_hi; r += 2) {
+    // the four units of an m-block take its row pairs in turn (pairs 0, 4, 8, ... / 1, 5, 9, ... / ...), so a block with few
+    // valid rows (decode) is still spread over four warps
+    const int mb = u >> 2;
+    const int r_hi = g1.mblock_valid[mb];
+    for (int r = 2 * (u & 3); r < r_hi; r += 8) {
         uint4 buf[2][8];
         float inv[2], sc2[2];
 #pragma unroll
@@ -348,6 +351,19 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
     const int arrive_total_slot = static_cast<int>(rp.sl.pool_rows / MM_BLOCK_M);   // last word of the arrival array
 
     if (!fp.gemm_only) {
+    // While the routing steps below run (some 20 us of dependent round trips), start pulling the weights of the first GEMM1
+    // tiles into L2.  Which expert a tile belongs to is not known yet; with few tokens (the regime of this mode) every local
+    // expert that has rows has ONE m-block, so tile t most likely is expert t / nb1 -- a wrong guess only costs L2 traffic.
+    if (tid == 0) {
+        const int nb1_ = fp.g1.n_blocks, kb_ = fp.g1.kdim / kBlockK;
+        for (int t = blockIdx.x; t < 96; t += gridDim.x) {          // 96 tiles of 1 MiB: what L2 can hold on to until they are used
+            const int e = t / nb1_;
+            if (e >= rp.E_loc) break;
+            const uint8_t* wt = fp.w1_tiled + static_cast<int64_t>(t) * kb_ * kBBytes;     // tile t of [expert][n block][k block][256][128]
+            for (int kb = 0; kb < kb_; ++kb)
+                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(wt + static_cast<int64_t>(kb) * kBBytes), "r"(kBBytes) : "memory");
+        }
+    }
     // ------------------------------------------------------------------ phase 1: local histogram, publish counts
     // This CTA pushes the contiguous share [lo, hi) of the rank's routes; `before` counts, per expert, the valid routes
     // in front of the share, so the CTA can number its routes without talking to the other CTAs.
@@ -651,7 +667,7 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
         //     the helper warps of the whole grid walk it front to back together.  After a chunk's rows are written: warp
         //     barrier, one system-scope fence, then one arrival per row on the owner (per m-block and in total).
         // (b) requantisation units, claimed in m-block order by the helper warps of all CTAs: once every GEMM1 tile of the
-        //     m-block is stored (each of the 8 epilogue warps of each of its nb1 tiles counts once), turn 32 of its bf16 rows
+        //     m-block is stored (each of the 8 epilogue warps of each of its nb1 tiles counts once), turn a quarter of its bf16 rows
         //     into e4m3 with one scale per row (deep_gemm/include/deep_gemm/impls/mega_moe_dcu_tiles.cuh:672-733) and count
         //     the quarter towards l2_ready[m-block].
         // Both loops are kept as simple as this on purpose: merged into one loop the compiler spills the row buffers and the

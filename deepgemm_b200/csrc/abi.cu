@@ -129,6 +129,13 @@ int sm_count(int* out) {
     return 0;
 }
 
+// Launch of the layer kernel: one CTA per SM, and its CTAs wait on one another, so all of them have to be resident.  The
+// default is a cooperative launch, which guarantees that (or fails).  MEGAMOE_COOPERATIVE_LAUNCH=0 selects an ordinary
+// launch of exactly one CTA per SM after an occupancy check (226 KiB of shared memory: a second CTA cannot share an SM);
+// it is resident as soon as the SMs are free of other kernels, and until then its waits spin -- bounded, so the worst case
+// is an error status, not a hang.
+int fused_resident_ctas(int sms, int* out);
+
 int ensure_gemm_attrs() {
     static std::mutex mu;
     static bool done[64] = {false};
@@ -142,6 +149,21 @@ int ensure_gemm_attrs() {
     MM_CUDA(cudaFuncSetAttribute(mm::grouped_gemm_pair_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, mm::kPairSmemBytes));
     MM_CUDA(cudaFuncSetAttribute(mm::grouped_gemm_pair_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, mm::kPairSmemBytes));
     if (dev < 64) done[dev] = true;
+    return 0;
+}
+
+int fused_resident_ctas(int sms, int* out) {
+    static std::mutex mu;
+    static int cached[64] = {0};
+    int dev = 0;
+    MM_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lk(mu);
+    if (dev < 64 && cached[dev]) { *out = cached[dev]; return 0; }
+    int per_sm = 0;
+    MM_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, mm::mega_moe_fused_kernel, mm::kFusedThreads, mm::kGemmSmemBytes));
+    const int n = per_sm * sms;
+    if (dev < 64) cached[dev] = n;
+    *out = n;
     return 0;
 }
 
@@ -172,6 +194,21 @@ int pair_cluster_count(int sms, int* out) {
     if (dev < 64) cached[dev] = n > 0 ? n : -1;
     if (getenv("MEGAMOE_VERBOSE")) fprintf(stderr, "megamoe: %d resident CTA pairs on %d SMs (device %d)\n", n, sms, dev);
     *out = n;
+    return 0;
+}
+
+int launch_layer_kernel(int sms, void** args, const CUtensorMap& tm_pool, const CUtensorMap& tm_w1, const CUtensorMap& tm_act,
+                        const CUtensorMap& tm_w2, const mm::FusedParams& fp, cudaStream_t stream) {
+    static const bool cooperative = [] { const char* v = getenv("MEGAMOE_COOPERATIVE_LAUNCH"); return !(v && v[0] == '0'); }();
+    if (cooperative) {
+        MM_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(mm::mega_moe_fused_kernel), dim3(sms), dim3(mm::kFusedThreads),
+                                            args, mm::kGemmSmemBytes, stream));
+        return 0;
+    }
+    int resident = 0;
+    if (int rc = fused_resident_ctas(sms, &resident)) return rc;
+    MM_REQUIRE(resident >= sms, "the layer kernel needs one resident CTA per SM (%d), the device offers %d", sms, resident);
+    mm::mega_moe_fused_kernel<<<sms, mm::kFusedThreads, mm::kGemmSmemBytes, stream>>>(tm_pool, tm_w1, tm_act, tm_w2, fp);
     return 0;
 }
 
@@ -578,8 +615,7 @@ int mm_fp8_w8a8_mega_moe(void* y, const void* w1, const float* s1, const void* w
     if (mode == MM_MODE_FUSED) {
         if (int rc = stage_begin(stream)) return rc;
         // cooperative launch: all CTAs must be resident because they wait on one another
-        MM_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(mm::mega_moe_fused_kernel), dim3(sms), dim3(mm::kFusedThreads),
-                                            fused_args, mm::kGemmSmemBytes, stream));
+        if (int rc = launch_layer_kernel(sms, fused_args, tm_pool, tm_w1, tm_act, tm_w2, fp, stream)) return rc;
         MM_LAUNCHED();
         if (int rc = stage_end(MM_STAGE_FUSED, stream)) return rc;
         return 0;
@@ -601,8 +637,7 @@ int mm_fp8_w8a8_mega_moe(void* y, const void* w1, const float* s1, const void* w
         mm::send_plan_kernel<<<route_blocks, MM_ROUTE_CHUNK, 0, stream>>>(rp);
         MM_STAGE(MM_STAGE_DISPATCH);
         fp.gemm_only = 1;
-        MM_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(mm::mega_moe_fused_kernel), dim3(sms), dim3(mm::kFusedThreads),
-                                            fused_args, mm::kGemmSmemBytes, stream));
+        if (int rc = launch_layer_kernel(sms, fused_args, tm_pool, tm_w1, tm_act, tm_w2, fp, stream)) return rc;
         MM_STAGE(MM_STAGE_FUSED);
         // the reduce kernel below leaves the per-m-block dependency counters zero for the next call: l1_done, l2_ready and
         // grid_sync are adjacent in the scratch buffer, the arrival counters live in the symmetric buffer

@@ -1,8 +1,9 @@
 // The layer's compute phase -- and, in MM_MODE_FUSED, the whole layer -- as ONE persistent, warp-specialised kernel.
 //
 // Replaces mega_moe_multirank_persistent_w8a8_channelwise_kernel
-// (deep_gemm/include/deep_gemm/impls/mega_moe_dcu.cuh:259-765).  One CTA per SM, launched cooperatively so that all
-// CTAs are resident (they wait on one another).  Warp roles of a CTA (384 threads):
+// (deep_gemm/include/deep_gemm/impls/mega_moe_dcu.cuh:259-765).  One CTA per SM; the CTAs wait on one another, so all of
+// them have to be resident: the host launches it cooperatively (or, on request, as exactly as many CTAs as SMs after an
+// occupancy check: a second CTA cannot share an SM with 226 KiB of shared memory).  Warp roles of a CTA (384 threads):
 //   warp 0      TMA producer: streams weight tiles and pool / activation tiles into the operand ring;
 //   warp 1      MMA issuer: tcgen05.mma into two TMEM accumulators;
 //   warps 2-3   helpers: (a) push routed rows to the owners' receive pools over NVLink, (b) requantise finished m-blocks;
@@ -32,7 +33,7 @@
 //     every GEMM1 tile of the m-block (the channelwise scale needs the whole row), converts bf16 -> e4m3, bumps l2_ready;
 //   - GEMM2 tile: the activation operand waits for l2_ready[m-block] == 4.
 // A tile only ever waits for work that belongs to tiles earlier in the order (or for pushes, which wait for nothing),
-// every role walks its items in order and all CTAs are resident, so the waits cannot form a cycle.  Every wait is
+// every role walks its items in order and all CTAs become resident, so the waits cannot form a cycle.  Every wait is
 // bounded and ends in a status code, never in a hang.
 #pragma once
 #include "gemm.cuh"
@@ -98,6 +99,20 @@ __device__ __forceinline__ bool wait_flag_ge(const int* flag, int target, bool s
         }
         __nanosleep(sleep_ns);
     }
+}
+
+// Ordering of pushed rows before their arrival signal, and the signal itself.  With one rank nothing leaves the GPU, so GPU
+// scope is enough -- and it matters: a system-scope fence also waits for PCIe traffic, so with host<->device copies running
+// in other streams (a serving loop that uploads the next batch while this one computes) it takes several times longer.
+__device__ __forceinline__ void fence_rows_pushed(bool multi_rank) {
+    if (multi_rank) __threadfence_system(); else __threadfence();
+}
+__device__ __forceinline__ void signal_row_arrived(int* counter, bool multi_rank) {
+    if (multi_rank) asm volatile("red.relaxed.sys.global.add.s32 [%0], 1;" ::"l"(counter) : "memory");
+    else asm volatile("red.relaxed.gpu.global.add.s32 [%0], 1;" ::"l"(counter) : "memory");
+}
+__device__ __forceinline__ int load_arrivals(const int* counter, bool multi_rank) {
+    return multi_rank ? ld_acquire_sys(counter) : ld_acquire_gpu(counter);
 }
 
 // Position of a tile index in the tile order.  A CTA's tile indices grow, so seek() only moves forward.
@@ -229,11 +244,11 @@ __device__ __forceinline__ void push_chunk(const FusedParams& fp, int j0, int ch
                                   static_cast<int64_t>(row) * sizeof(MmPoolMeta)) = *reinterpret_cast<uint4*>(&m);
     }
     __syncwarp();
-    __threadfence_system();
+    fence_rows_pushed(rp.R > 1);
     if (row >= 0) {
         int* arr = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(rp.peers[owner]) + rp.sl.pool_arrive);
-        asm volatile("red.relaxed.sys.global.add.s32 [%0], 1;" ::"l"(arr + row / MM_BLOCK_M) : "memory");
-        asm volatile("red.relaxed.sys.global.add.s32 [%0], 1;" ::"l"(arr + arrive_total_slot) : "memory");
+        signal_row_arrived(arr + row / MM_BLOCK_M, rp.R > 1);
+        signal_row_arrived(arr + arrive_total_slot, rp.R > 1);
     }
 }
 
@@ -517,7 +532,7 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
         // All rows of this warp are written: one system-scope fence (ordered after the other lanes' stores by the warp
         // barrier), then the arrival counters of all its rows, one row per lane, as relaxed reductions.
         __syncwarp();
-        __threadfence_system();
+        fence_rows_pushed(rp.R > 1);
         for (int i0 = lo + warp; i0 < hi; i0 += 32 * warps_per_cta) {
             const int i = i0 + lane * warps_per_cta;
             if (i < hi) {
@@ -525,8 +540,8 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
                 if (row >= 0) {
                     const int e = static_cast<int>(idx[i]);
                     int* arr = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(rp.peers[e / rp.E_loc]) + rp.sl.pool_arrive);
-                    asm volatile("red.relaxed.sys.global.add.s32 [%0], 1;" ::"l"(arr + row / MM_BLOCK_M) : "memory");
-                    asm volatile("red.relaxed.sys.global.add.s32 [%0], 1;" ::"l"(arr + arrive_total_slot) : "memory");
+                    signal_row_arrived(arr + row / MM_BLOCK_M, rp.R > 1);
+                    signal_row_arrived(arr + arrive_total_slot, rp.R > 1);
                 }
             }
         }
@@ -597,8 +612,8 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
                             all_ready = ld_acquire_gpu(fp.grid_sync + MM_SYNC_UNITS_DONE) - requant_units >= 0;
                             if (!all_ready) ok = wait_flag_ge(fp.l2_ready + mb, 4, false, status, g.timeout_ns, &seen);
                         } else {
-                            all_arrived = ld_acquire_sys(arrive + arrive_total_slot) - rows_expected >= 0;
-                            if (!all_arrived) ok = wait_flag_ge(arrive + mb, g.mblock_valid[mb], true, status, rp.barrier_timeout_ns, &seen);
+                            all_arrived = load_arrivals(arrive + arrive_total_slot, rp.R > 1) - rows_expected >= 0;
+                            if (!all_arrived) ok = wait_flag_ge(arrive + mb, g.mblock_valid[mb], rp.R > 1, status, rp.barrier_timeout_ns, &seen);
                         }
                         if (second) polled_g2 += global_timer_ns() - t_poll; else polled_g1 += global_timer_ns() - t_poll;
                         if (!ok) {
@@ -753,8 +768,8 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
                     if (!scout_all_ready && (scout_polls++ & 7) == 0) scout_all_ready = ld_acquire_gpu(fp.grid_sync + MM_SYNC_UNITS_DONE) - requant_units >= 0;
                     ok = scout_all_ready || ld_acquire_gpu(fp.l2_ready + mb) - 4 >= 0;
                 } else {
-                    if (!scout_all_arrived && (scout_polls++ & 7) == 0) scout_all_arrived = ld_acquire_sys(arrive + arrive_total_slot) - rows_expected >= 0;
-                    ok = scout_all_arrived || ld_acquire_sys(arrive + mb) - g1.mblock_valid[mb] >= 0;
+                    if (!scout_all_arrived && (scout_polls++ & 7) == 0) scout_all_arrived = load_arrivals(arrive + arrive_total_slot, rp.R > 1) - rows_expected >= 0;
+                    ok = scout_all_arrived || load_arrivals(arrive + mb, rp.R > 1) - g1.mblock_valid[mb] >= 0;
                 }
                 if (!ok) break;
                 ++scout_n;
@@ -836,7 +851,7 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
         if (pending_mb >= 0 && lane == 0) { __threadfence(); red_release_gpu_add(fp.l1_done + pending_mb, 1); }
     }
 
-    __threadfence_system();
+    fence_rows_pushed(rp.R > 1);      // the combine stores of this CTA's GEMM2 tiles, before anybody is told they are done
     __syncthreads();
     if (tid == 0) stamp(9);
     // gemm_only: the combine barrier, the reduce and the counter reset are separate launches after this kernel

@@ -52,7 +52,7 @@ def measured_bf16_tflops():
     return None
 
 
-def parity_block(dist, group, rank, world, dev, sb, l1, l2, y, stats, tokens, n_samples=PARITY_SAMPLES):
+def parity_block(dist, group, rank, world, dev, sb, l1, l2, y, stats, tokens, n_samples=PARITY_SAMPLES, oracle_variant="fused"):
     """Correctness of the run that was just timed, computed outside the timed region at every N:
       counts_equal      per-expert receive statistics == bincount of all ranks' top-k indices (bit-exact routing counts);
       max_abs_over_rms, cosine   of `n_samples` tokens per rank against the CPU oracle (oracle/moe_oracle.py) run on just those
@@ -102,7 +102,7 @@ def parity_block(dist, group, rank, world, dev, sb, l1, l2, y, stats, tokens, n_
         w1p = megamoe.unpack_weights_tiled(l1[0][sel], "l1", 2 * I).cpu()
         w2p = megamoe.unpack_weights_tiled(l2[0][sel], "l2", H).cpu()
         _, lay, tr = orc.moe_layer([xq], [xs], [idx_local], [w_s], [w1p], [l1[1][sel].cpu()], [w2p], [l2[1][sel].cpu()],
-                                   int(touched.numel()), None, "fused", trace=True)
+                                   int(touched.numel()), None, oracle_variant, trace=True)
         rows = torch.from_numpy((lay.row_src_rank[0] >= 0).nonzero()[0])
         tt = torch.from_numpy(lay.row_src_token[0][rows.numpy()].astype("int64"))
         kk = torch.from_numpy(lay.row_src_slot[0][rows.numpy()].astype("int64"))
@@ -121,7 +121,7 @@ def parity_block(dist, group, rank, world, dev, sb, l1, l2, y, stats, tokens, n_
         dist.all_reduce(vals, op=dist.ReduceOp.MAX)
     err, cos, bad_counts = float(vals[0]), -float(vals[1]), float(vals[2]) > 0
     return {"counts_equal": not bad_counts, "max_abs_over_rms": round(err, 5), "cosine": round(cos, 7),
-            "sampled_tokens_per_rank": n_samples, "oracle": "oracle/moe_oracle.py, numerics 'fused', on the sampled tokens",
+            "sampled_tokens_per_rank": n_samples, "oracle": f"oracle/moe_oracle.py, numerics '{oracle_variant}', on the sampled tokens",
             "literal_bar": {"max_abs_over_rms": 2e-2, "cosine": 0.999, "met": bool(err <= 2e-2 and cos >= 0.999)},
             "ok": bool((not bad_counts) and cos >= 0.999 and err <= 0.1)}
 
@@ -456,6 +456,9 @@ def main():
     ap.add_argument("--split-baseline", action="store_true",
                     help="one GPU: time the reference test's split pipeline (scatter, grouped GEMM, SwiGLU+quantise, grouped GEMM, "
                          "gather) built from this library's kernels next to the layer call, on the same inputs")
+    ap.add_argument("--recipe", default="channelwise", choices=["channelwise", "ue8m0"],
+                    help="activation recipe between the GEMMs: the reference's channelwise fp32 scales (default) or per-32 UE8M0 scales "
+                         "applied by a block-scaled MMA (staged launches; parity is then checked against the oracle's ue8m0 variant)")
     ap.add_argument("--profile-only", action="store_true",
                     help="device-resident arm only (no end-to-end arm, no parity or CPU baseline): the command line for ncu captures")
     ap.add_argument("--sweep", default=None, help="comma-separated tokens-per-rank list: run the scaling sweep instead of the bench")
@@ -493,8 +496,12 @@ def main():
     def quantise_into_buffer(src):
         _lib.check(lib.mm_quant_per_token(src.data_ptr(), T, H, sb.x.data_ptr(), sb.x_sf.data_ptr(), stream))
 
+    recipe_kw = {"recipe": megamoe.RECIPE_UE8M0_PER32} if args.recipe == "ue8m0" else {}
+    if args.recipe == "ue8m0":
+        variant = "staged-ue8m0"
+
     def layer():
-        megamoe.fp8_w8a8_mega_moe(y, l1, l2, sb)
+        megamoe.fp8_w8a8_mega_moe(y, l1, l2, sb, **recipe_kw)
 
     def barrier():
         torch.cuda.synchronize()
@@ -576,7 +583,7 @@ def main():
         ev_free[b].record(s_main)
         s_main.wait_event(ev_out[b])                      # the previous y in this buffer has left the device
         if compute:
-            megamoe.fp8_w8a8_mega_moe(dy[b], l1, l2, sb)
+            megamoe.fp8_w8a8_mega_moe(dy[b], l1, l2, sb, **recipe_kw)
         ev_done[b].record(s_main)
         with torch.cuda.stream(s_out):
             s_out.wait_event(ev_done[b])
@@ -614,12 +621,13 @@ def main():
             acc[k_] = acc.get(k_, 0.0) + v / n_rep
     lib.mm_set_stage_timing(0)
     stats = torch.zeros((e_loc,), dtype=torch.int32, device=dev)
-    megamoe.fp8_w8a8_mega_moe(y, l1, l2, sb, cumulative_local_expert_recv_stats=stats)
+    megamoe.fp8_w8a8_mega_moe(y, l1, l2, sb, cumulative_local_expert_recv_stats=stats, **recipe_kw)
     torch.cuda.synchronize()
     sb.check_status()
     rows_recv = int(stats.sum().item())
     touched = int((stats > 0).sum().item())
-    parity = parity_block(dist, group, rank, world, dev, sb, l1, l2, y, stats, T, min(PARITY_SAMPLES, T))
+    parity = parity_block(dist, group, rank, world, dev, sb, l1, l2, y, stats, T, min(PARITY_SAMPLES, T),
+                          oracle_variant="ue8m0" if args.recipe == "ue8m0" else "fused")
 
     # ---- roofline of the dominant kernel ----------------------------------------------------------------------------
     split = "gemm1" in acc        # separate GEMM1 / requantisation / GEMM2 launches (MEGAMOE_STAGED_SPLIT=1)
@@ -630,6 +638,9 @@ def main():
         kernel_bytes = touched * (2 * I * H + 4 * 2 * I) + rows_recv * (H + 16) + rows_recv * I * 2
         kernel_flops = rows_recv * 2 * H * 2 * I
         kernel_name = "grouped_gemm_kernel<0> (GEMM1 + SwiGLU)"
+        if args.recipe == "ue8m0":             # codes and scale bytes instead of bf16 activations
+            kernel_bytes = touched * (2 * I * H + 4 * 2 * I) + rows_recv * (H + 16) + rows_recv * (I + I // 32)
+            kernel_name = "grouped_gemm_kernel<2> (GEMM1 + SwiGLU + per-32 UE8M0 quantisation)"
     else:
         # the layer kernel moves the whole layer's bytes (formula of the reference's own test,
         # tests/test_mega_moe_dcu.py:352-364): weights + scales, FP8 rows in, FP8 activations written and read, bf16 rows out

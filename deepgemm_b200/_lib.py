@@ -16,8 +16,8 @@ SYM_NAMES = ["peer_ptrs", "signals", "runtime_num_tokens", "count_matrix", "x", 
              "pool_x", "pool_meta", "combine", "pool_rows"]
 SCR_NAMES = ["status", "epoch", "plan", "block_counts", "dest_base", "expert_total", "expert_off", "mblock_expert",
              "mblock_valid", "dest_row", "row_amax", "act_scale", "act_bf16", "act_fp8", "send_base", "send_list", "l1_done",
-             "l2_ready", "grid_sync", "route_blocks"]
-MODE_STAGED, MODE_FUSED, MODE_STAGED_SPLIT = 0, 1, 2
+             "l2_ready", "grid_sync", "act_sf", "route_blocks"]
+MODE_STAGED, MODE_FUSED, MODE_STAGED_SPLIT, MODE_STAGED_UE8M0 = 0, 1, 2, 3
 MAX_RANKS = 16
 BLOCK_M = 128
 

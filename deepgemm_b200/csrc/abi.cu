@@ -16,6 +16,7 @@
 #include "fused.cuh"
 #include "gemm.cuh"
 #include "gemm_pair.cuh"
+#include "gemm_ue8m0.cuh"
 #include "layout.h"
 #include "misc.cuh"
 #include "probe.cuh"
@@ -145,6 +146,8 @@ int ensure_gemm_attrs() {
     if (dev < 64 && done[dev]) return 0;
     MM_CUDA(cudaFuncSetAttribute(mm::grouped_gemm_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, mm::kGemmSmemBytes));
     MM_CUDA(cudaFuncSetAttribute(mm::grouped_gemm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, mm::kGemmSmemBytes));
+    MM_CUDA(cudaFuncSetAttribute(mm::grouped_gemm_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, mm::kGemmSmemBytes));
+    MM_CUDA(cudaFuncSetAttribute(mm::grouped_gemm_ue8m0_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, mm::kU8SmemBytes));
     MM_CUDA(cudaFuncSetAttribute(mm::mega_moe_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, mm::kGemmSmemBytes));
     MM_CUDA(cudaFuncSetAttribute(mm::grouped_gemm_pair_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, mm::kPairSmemBytes));
     MM_CUDA(cudaFuncSetAttribute(mm::grouped_gemm_pair_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, mm::kPairSmemBytes));
@@ -286,6 +289,7 @@ int mm_scratch_layout(int R, int E, int T, int K, int H, int I, int64_t* offsets
         offsets[MM_SCR_ACT_BF16] = L.act_bf16; offsets[MM_SCR_ACT_FP8] = L.act_fp8; offsets[MM_SCR_ROUTE_BLOCKS] = L.route_blocks;
         offsets[MM_SCR_SEND_BASE] = L.send_base; offsets[MM_SCR_SEND_LIST] = L.send_list;
         offsets[MM_SCR_L1_DONE] = L.l1_done; offsets[MM_SCR_L2_READY] = L.l2_ready; offsets[MM_SCR_GRID_SYNC] = L.grid_sync;
+        offsets[MM_SCR_ACT_SF] = L.act_sf;
     }
     if (total_bytes) *total_bytes = L.total;
     return 0;
@@ -536,7 +540,7 @@ int mm_fp8_w8a8_mega_moe(void* y, const void* w1, const float* s1, const void* w
     MM_REQUIRE(num_tokens >= 0 && num_tokens <= T_max, "too many tokens");
     MM_REQUIRE(peer_ptrs[rank] == reinterpret_cast<uint64_t>(sym_base), "peer_ptrs[rank] must be the local buffer");
     MM_REQUIRE(!isnan(activation_clamp) && activation_clamp > 0.0f, "activation_clamp must be positive (+inf for none)");
-    MM_REQUIRE(mode == MM_MODE_STAGED || mode == MM_MODE_FUSED || mode == MM_MODE_STAGED_SPLIT, "unknown mode");
+    MM_REQUIRE(mode == MM_MODE_STAGED || mode == MM_MODE_FUSED || mode == MM_MODE_STAGED_SPLIT || mode == MM_MODE_STAGED_UE8M0, "unknown mode");
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
 
     mm::RouteParams rp;
@@ -673,6 +677,22 @@ int mm_fp8_w8a8_mega_moe(void* y, const void* w1, const float* s1, const void* w
         if (clusters < sms / 4) pair_gemms = false;      // too few resident pairs to be worth it
         pair_grid = 2 * clusters;
     }
+    if (mode == MM_MODE_STAGED_UE8M0) {
+        // UE8M0 recipe: GEMM1 quantises in its epilogue (codes into the FP8 activation region, scale bytes beside them),
+        // GEMM2 applies the block scales in the tensor core: no bf16 activations, no requantisation launch
+        MM_REQUIRE(H % 128 == 0 && I % 128 == 0, "the UE8M0 recipe needs hidden sizes that are multiples of 128");
+        CUtensorMap tm_w2q;
+        if (int rc = tensor_map_2d(w2, 128, (uint64_t)E_loc * ((H + 255) / 256) * (I / 128) * 256, 128, &tm_w2q)) return rc;
+        mm::GemmParams u1 = g1, u2 = g2;
+        u1.act_q_out = sc + rp.cl.act_fp8;
+        u1.act_sf = sc + rp.cl.act_sf;
+        u2.act_sf = sc + rp.cl.act_sf;
+        u2.n_blocks = H / 128;
+        mm::grouped_gemm_kernel<2><<<sms, mm::kGemmThreads, mm::kGemmSmemBytes, stream>>>(tm_pool, tm_w1, u1);
+        MM_STAGE(MM_STAGE_GEMM1);
+        mm::grouped_gemm_ue8m0_kernel<<<sms, mm::kGemmThreads, mm::kU8SmemBytes, stream>>>(tm_act, tm_w2q, u2);
+        MM_STAGE(MM_STAGE_GEMM2);
+    } else {
     if (pair_gemms) mm::grouped_gemm_pair_kernel<0><<<pair_grid, mm::kGemmThreads, mm::kPairSmemBytes, stream>>>(tm_pool, tm_w1h, g1);
     else mm::grouped_gemm_kernel<0><<<sms, mm::kGemmThreads, mm::kGemmSmemBytes, stream>>>(tm_pool, tm_w1, g1);
     MM_STAGE(MM_STAGE_GEMM1);
@@ -682,6 +702,7 @@ int mm_fp8_w8a8_mega_moe(void* y, const void* w1, const float* s1, const void* w
     if (pair_gemms) mm::grouped_gemm_pair_kernel<1><<<pair_grid, mm::kGemmThreads, mm::kPairSmemBytes, stream>>>(tm_act, tm_w2h, g2);
     else mm::grouped_gemm_kernel<1><<<sms, mm::kGemmThreads, mm::kGemmSmemBytes, stream>>>(tm_act, tm_w2, g2);
     MM_STAGE(MM_STAGE_GEMM2);
+    }   // channelwise recipe
     }   // split launches
     // the reduce kernel does the cross-rank "combine stores done" barrier itself before it reads the combine buffer
     mm::combine_reduce_kernel<<<sms * 8, 256, 0, stream>>>(rp, static_cast<__nv_bfloat16*>(y), R > 1 ? 1 : 0, reset_a, reset_a_words,

@@ -3,6 +3,8 @@
 //   kind 0 (GEMM1): act[row, j] = bf16( silu(g) * u * w_route ),  g = acc_gate * (sx[row] * s1[j]),  u likewise with
 //                   weight row I + j; also the per-row amax of the bf16 values.  Replaces
 //                   deep_gemm/include/deep_gemm/impls/mega_moe_dcu_tiles.cuh:380-670 (compute_route_mmac_mtile16_l1_chunk).
+//   kind 2 (GEMM1, UE8M0 recipe): the same SwiGLU value in fp32, quantised in the epilogue with one power-of-two scale
+//                   per (row, 32 columns): codes e4m3(a * 2^-e), scale byte e + 127 (gemm_ue8m0.cuh consumes them).
 //   kind 1 (GEMM2): out[row, h] = bf16( acc * (s2[row] * sw2[h]) ) stored straight into combine[token][slot][:] of the
 //                   SOURCE rank over NVLink.  Replaces impls/mega_moe_dcu_tiles.cuh:735-1163.
 //
@@ -12,6 +14,7 @@
 // For kind 0 the 256 weight rows are 128 gate rows and the 128 matching up rows, so one tile yields 128 SwiGLU outputs.
 #pragma once
 #include <cuda_bf16.h>
+#include <cuda_fp8.h>
 #include "layout.h"
 #include "ptx.cuh"
 
@@ -50,6 +53,9 @@ struct GemmParams {
     __nv_bfloat16* act_bf16;   // [pool_rows][I]
     unsigned int* row_amax;
     float clamp;               // +inf = none
+    // kind 2 (GEMM1 with per-(row, 32 columns) UE8M0 activation scales): FP8 codes and scale bytes, no bf16 round trip
+    uint8_t* act_q_out;        // [pool_rows][I] e4m3
+    uint8_t* act_sf;           // [m-blocks][I / 128][512]: scale bytes of 128 rows x 4 column blocks, byte (r % 32) * 16 + (r / 32) * 4 + block
     // kind 1
     const float* act_scale;    // [pool_rows]
     __nv_bfloat16* out_rows;   // null: store into the source ranks' combine buffers; else out_rows[row][n_out] (plain grouped GEMM)
@@ -92,7 +98,7 @@ __device__ __forceinline__ void epilogue_math(const GemmParams& p, uint32_t tmem
     // Each pass handles one 128-byte output segment (64 bf16) per row: two 32-column chunks, staged in shared
     // memory (16-byte pieces XOR-swizzled by row so neither phase has bank conflicts), then written so that
     // 8 lanes cover one row's segment.
-    constexpr int kPasses = (kKind == 0) ? 1 : 2;
+    constexpr int kPasses = (kKind == 1) ? 2 : 1;
     float amax = 0.0f;
 #pragma unroll 1
     for (int pass = 0; pass < kPasses; ++pass) {
@@ -101,6 +107,47 @@ __device__ __forceinline__ void epilogue_math(const GemmParams& p, uint32_t tmem
         for (int sub = 0; sub < 2; ++sub) {
             const int c = seg_idx * 2 + sub;             // 32-column chunk of outputs
             uint32_t packed[16];
+            if (kKind == 2) {
+                // UE8M0 recipe: this thread holds the 32 columns of one scale block of its row
+                uint32_t g[32], u[32];
+                tmem_ld_32x32(t_addr + c * 32, g);
+                tmem_ld_32x32(t_addr + 128 + c * 32, u);
+                tmem_ld_wait();
+                float o[32];
+                float bmax = 0.0f;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    float gv = __uint_as_float(g[j]) * (row_scale * sc[c * 32 + j]);
+                    float uv = __uint_as_float(u[j]) * (row_scale * sc[128 + c * 32 + j]);
+                    if (do_clamp) {
+                        gv = fminf(fmaxf(gv, -p.clamp), p.clamp);
+                        uv = fminf(fmaxf(uv, -p.clamp), p.clamp);
+                    }
+                    o[j] = silu_f(gv) * uv * route_w;
+                    bmax = fmaxf(bmax, fabsf(o[j]));
+                }
+                // smallest power of two 2^e with bmax <= 448 * 2^e, on the float bits: 448 = 1.75 * 2^8
+                const uint32_t bits = __float_as_uint(bmax);
+                int byte = static_cast<int>((bits >> 23) & 0xffu) - 8 + ((bits & 0x7fffffu) > 0x600000u ? 1 : 0);
+                byte = min(max(byte, 1), 253);
+                const float inv = __uint_as_float(static_cast<uint32_t>(254 - byte) << 23);
+                uint32_t q8[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(o[4 * j] * inv, o[4 * j + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+                    const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(o[4 * j + 2] * inv, o[4 * j + 3] * inv), __NV_SATFINITE, __NV_E4M3);
+                    q8[j] = lo | (hi << 16);
+                }
+                if (row_ok) {
+                    uint4* dst = reinterpret_cast<uint4*>(p.act_q_out + static_cast<int64_t>(row) * p.n_out + nb * 128 + c * 32);
+                    dst[0] = make_uint4(q8[0], q8[1], q8[2], q8[3]);
+                    dst[1] = make_uint4(q8[4], q8[5], q8[6], q8[7]);
+                }
+                // scale byte of (row, block c): rows past the valid count get 1.0 so that nothing undefined reaches the MMA
+                p.act_sf[(static_cast<int64_t>(mb) * p.n_blocks + nb) * 512 + lane * 16 + q * 4 + c] =
+                    static_cast<uint8_t>(row_ok ? byte : 127);
+                continue;
+            }
             if (kKind == 0) {
                 uint32_t g[32], u[32];
                 tmem_ld_32x32(t_addr + c * 32, g);
@@ -141,6 +188,7 @@ __device__ __forceinline__ void epilogue_math(const GemmParams& p, uint32_t tmem
                     make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
             }
         }
+        if (kKind == 2) continue;                        // codes and scale bytes were written directly
         __syncwarp();
         const int col0 = (kKind == 0 ? nb * 128 : nb * kBlockN) + seg_idx * 64;   // first output column of the segment
 #pragma unroll
@@ -292,7 +340,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             {
                 const int t = (warp - 2) * 32 + lane;
                 const float* ws = p.w_scale + static_cast<int64_t>(e) * p.w_rows_per_expert;
-                if (kKind == 0) {
+                if (kKind != 1) {
                     sc[t] = t < 128 ? ws[nb * 128 + t] : ws[p.w_rows_per_expert / 2 + nb * 128 + (t - 128)];
                 } else {
                     const int c0 = nb * kBlockN + t;
@@ -303,7 +351,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             float row_scale = 0.0f, route_w = 0.0f;
             uint8_t* out_ptr = nullptr;                // kind 1: destination row in the source rank's combine buffer
             if (row_ok) {
-                if (kKind == 0) {
+                if (kKind != 1) {
                     const MmPoolMeta m = p.meta[row];
                     row_scale = m.x_scale;
                     route_w = m.route_weight;

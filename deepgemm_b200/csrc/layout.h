@@ -83,6 +83,7 @@ struct MmScratchLayout {
     int64_t act_scale;     // f32   [pool_rows]
     int64_t act_bf16;      // bf16  [pool_rows][I]
     int64_t act_fp8;       // fp8   [pool_rows][I]
+    int64_t act_sf;        // u8    [pool_rows / 128][I / 128][512]  UE8M0 scale bytes of the block-scaled recipe (gemm_ue8m0.cuh)
     int64_t total;
     int64_t route_blocks;
 };
@@ -141,6 +142,7 @@ static inline MmScratchLayout mm_scratch_layout_of(int R, int E, int T, int K, i
     L.act_scale = o;     o = mm_align(o + pool_rows * 4, 256);
     L.act_bf16 = o;      o = mm_align(o + pool_rows * I * 2, 1024);
     L.act_fp8 = o;       o = mm_align(o + pool_rows * I, 1024);
+    L.act_sf = o;        o = mm_align(o + pool_rows / MM_BLOCK_M * (I / 128) * 512, 1024);
     L.total = o;
     return L;
 }

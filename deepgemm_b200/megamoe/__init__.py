@@ -42,6 +42,11 @@ _ALIASES = {_LARGE_OPT_ENV: "MEGAMOE_USE_STAGED", _LARGE_OPT_THRESHOLD_ENV: "MEG
 # over NVLink, runs GEMM1, requantises and runs GEMM2 with per-m-block dependencies; MEGAMOE_STAGED_SPLIT=1 selects separate
 # dispatch / barrier / GEMM1 / requantisation / GEMM2 launches instead.  All ranks of a group must use the same setting.
 _STAGED_SPLIT_ENV = "MEGAMOE_STAGED_SPLIT"
+# Recipe value of fp8_mega_moe for the activation recipe of the reference's Blackwell Mega MoE kernel (deep_gemm/mega/__init__.py:105-142,
+# deep_gemm/include/deep_gemm/impls/sm100_fp8_fp4_mega_moe.cuh:1023-1057): the SwiGLU output is quantised inside the GEMM1 tile
+# to e4m3 with one power-of-two (UE8M0) scale per (row, 32 columns) and GEMM2 applies the scales with a block-scaled MMA.
+# The default recipe (1, 1, 32) is the reference's W8A8 channelwise one.  Weights are FP8 with channelwise scales in both.
+RECIPE_UE8M0_PER32 = "ue8m0_per32"
 _FUSED_AVAILABLE = True
 
 
@@ -451,7 +456,7 @@ def _tiled_weight(w: torch.Tensor, rows: int, k: int, which: str) -> torch.Tenso
 
 def fp8_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer: SymmBuffer,
                  cumulative_local_expert_recv_stats: Optional[torch.Tensor] = None,
-                 recipe: Tuple[int, int, int] = (1, 1, 32), activation: str = "swiglu",
+                 recipe=(1, 1, 32), activation: str = "swiglu",
                  activation_clamp: Optional[float] = None, fast_math: bool = True, big_fused_cuda_graph: bool = False,
                  stages_fused_cuda_graph: bool = False, dispatch_num_tokens: Optional[int] = None) -> None:
     """The W8A8 channelwise Mega MoE layer, in place into `y` (megamoe/__init__.py:328-449 and
@@ -490,8 +495,14 @@ def fp8_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer: SymmBuffer
         split_tokens = dispatch_tokens
 
     # argument checks of csrc/apis/mega_dcu.hpp:355-445
-    if tuple(recipe) != (1, 1, 32):
-        raise RuntimeError("DCU W8A8 MegaMoE expects recipe=(1,1,32)")
+    ue8m0 = isinstance(recipe, str) and recipe == RECIPE_UE8M0_PER32
+    if not ue8m0 and (isinstance(recipe, str) or tuple(recipe) != (1, 1, 32)):
+        raise RuntimeError(f"DCU W8A8 MegaMoE expects recipe=(1,1,32) (or recipe={RECIPE_UE8M0_PER32!r} for per-32 UE8M0 "
+                           "activation scales)")
+    if ue8m0:
+        if graph_mode and not stages_fused_cuda_graph:
+            raise ValueError("the UE8M0 recipe runs as staged launches: use stages_fused_cuda_graph=True for graph capture")
+        staged = True
     if activation != "swiglu":
         raise RuntimeError("DCU W8A8 MegaMoE supports swiglu only")
     if not fast_math:
@@ -541,8 +552,9 @@ def fp8_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer: SymmBuffer
             call_y.data_ptr(), w1.data_ptr(), l1_sf.contiguous().data_ptr(), w2.data_ptr(), l2_sf.contiguous().data_ptr(),
             stats_ptr, sb.buffer.data_ptr(), sb.route_scratch.data_ptr(), sb._peer_array, sb.rank, sb.num_ranks,
             sb.num_max_tokens_per_rank, e_loc, num_tokens, sb.num_topk, hidden, inter, clamp,
-            (_lib.MODE_STAGED_SPLIT if _staged_as_split_launches(sb, split_tokens, e_loc) else _lib.MODE_STAGED)
-            if staged else _lib.MODE_FUSED, runtime_ptr, _stream_ptr()))
+            _lib.MODE_STAGED_UE8M0 if ue8m0 else
+            ((_lib.MODE_STAGED_SPLIT if _staged_as_split_launches(sb, split_tokens, e_loc) else _lib.MODE_STAGED)
+             if staged else _lib.MODE_FUSED), runtime_ptr, _stream_ptr()))
 
 
 fp8_w8a8_mega_moe = fp8_mega_moe
@@ -743,4 +755,5 @@ __all__ = [
     "fp8_mega_moe",
     "fp8_w8a8_mega_moe",
     "fill_inputs_from_router",
+    "RECIPE_UE8M0_PER32",
 ]

@@ -30,7 +30,7 @@ enum {
     MM_SCR_STATUS = 0, MM_SCR_EPOCH, MM_SCR_PLAN, MM_SCR_BLOCK_COUNTS, MM_SCR_DEST_BASE, MM_SCR_EXPERT_TOTAL,
     MM_SCR_EXPERT_OFF, MM_SCR_MBLOCK_EXPERT, MM_SCR_MBLOCK_VALID, MM_SCR_DEST_ROW, MM_SCR_ROW_AMAX,
     MM_SCR_ACT_SCALE, MM_SCR_ACT_BF16, MM_SCR_ACT_FP8, MM_SCR_SEND_BASE, MM_SCR_SEND_LIST, MM_SCR_L1_DONE, MM_SCR_L2_READY,
-    MM_SCR_GRID_SYNC, MM_SCR_ROUTE_BLOCKS, MM_SCR_NUM_OFFSETS
+    MM_SCR_GRID_SYNC, MM_SCR_ACT_SF, MM_SCR_ROUTE_BLOCKS, MM_SCR_NUM_OFFSETS
 };
 /* stages of one staged layer call, in launch order (indices of mm_get_stage_times) */
 enum {
@@ -39,7 +39,7 @@ enum {
     MM_STAGE_FUSED /* the single launch of MM_MODE_FUSED */, MM_NUM_STAGES
 };
 /* execution variants of mm_fp8_w8a8_mega_moe */
-enum { MM_MODE_STAGED = 0, MM_MODE_FUSED = 1, MM_MODE_STAGED_SPLIT = 2 };
+enum { MM_MODE_STAGED = 0, MM_MODE_FUSED = 1, MM_MODE_STAGED_SPLIT = 2, MM_MODE_STAGED_UE8M0 = 3 };
 
 /* Message of the last failure on this thread. */
 const char* mm_last_error(void);
@@ -93,7 +93,11 @@ int mm_router_topk_quant(const void* x_bf16, const float* router_logits, int num
  * MMAC units instead, deep_gemm/include/deep_gemm/layout/mega_moe_dcu.cuh:50-66.)  stats (nullable) int32 [E_loc] accumulates rows received per local
  * expert.  peer_ptrs: HOST array of the R ranks' symmetric-buffer device addresses (entry `rank` is sym_base).
  * runtime_num_tokens (nullable): device int32 overriding num_tokens (CUDA-graph bucket mode).
- * activation_clamp: +inf for none.  mode: MM_MODE_STAGED or MM_MODE_FUSED.
+ * activation_clamp: +inf for none.  mode: MM_MODE_FUSED (one launch, small token counts), MM_MODE_STAGED (routing kernels + the
+ * layer kernel), MM_MODE_STAGED_SPLIT (separate dispatch / GEMM1 / requantisation / GEMM2 launches), or MM_MODE_STAGED_UE8M0:
+ * split launches with the activation recipe of the reference's Blackwell kernel -- e4m3 codes with one power-of-two (UE8M0)
+ * scale per (row, 32 columns), produced in the GEMM1 epilogue and applied by a block-scaled MMA in GEMM2
+ * (deep_gemm/include/deep_gemm/impls/sm100_fp8_fp4_mega_moe.cuh:839-870,1023-1057); weights stay FP8 with channelwise scales.
  * Replaces launch_mega_moe_multirank_persistent_hip_w8a8_channelwise, csrc/apis/mega_dcu.hpp:41-55, and the
  * staged driver fp8_mega_moe_large_opt_3stage, megamoe/large_opt.py:367-508. */
 int mm_fp8_w8a8_mega_moe(void* y, const void* w1, const float* s1, const void* w2, const float* s2, int* stats,

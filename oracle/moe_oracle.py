@@ -255,6 +255,28 @@ class LayerTrace:
     out_rows: List[torch.Tensor] = field(default_factory=list)  # bf16 per-route outputs in pool-row order
 
 
+def ue8m0_block_quant(act: torch.Tensor, block: int = 32):
+    """Per-(row, 32-column block) power-of-two scales, the activation recipe of the reference's Blackwell kernel
+    (deep_gemm/include/deep_gemm/impls/sm100_fp8_fp4_mega_moe.cuh:1023-1057: per-32 amax -> UE8M0 scale -> e4m3 pack):
+    the scale is the smallest power of two 2^e with amax <= 448 * 2^e, stored as the byte e + 127 (clamped to 1..253);
+    codes = e4m3(act * 2^-e), saturating.  Computed on the float bits, so it is exact and reproducible:
+    amax = 1.f * 2^(x-127) needs e = x - 135 when f <= 0.75 (448 = 1.75 * 2^8) and one more otherwise.
+    Returns (codes e4m3 [rows, n], scale bytes uint8 [rows, n / block])."""
+    rows, n = act.shape
+    a = act.float().reshape(rows, n // block, block)
+    amax = a.abs().amax(dim=2).contiguous()
+    bits = amax.view(torch.int32)
+    byte = ((bits >> 23) & 0xFF) - 8 + ((bits & 0x7FFFFF) > 0x600000).to(torch.int32)
+    byte = byte.clamp(1, 253)
+    inv = ((254 - byte) << 23).view(torch.float32)          # 2^-(byte - 127), exact
+    q = (a * inv.unsqueeze(2)).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn).reshape(rows, n)
+    return q, byte.to(torch.uint8)
+
+
+def ue8m0_to_float(byte: torch.Tensor) -> torch.Tensor:
+    return (byte.to(torch.int32) << 23).view(torch.float32)
+
+
 def swiglu_quant_channelwise(gu: torch.Tensor, route_w: Optional[torch.Tensor], clamp: Optional[float]):
     """K2 of the staged path and of the split baseline (megamoe/dcu_megamoe_large_opt/K2_fused/k2_fused_ext.cu:254-377):
     gu [rows, 2I] holds bf16-representable gate | up values.  up is clamped two-sided, gate from above only;
@@ -292,7 +314,7 @@ def moe_layer(x_q: Sequence[torch.Tensor], x_scale: Sequence[torch.Tensor],
     per owner rank o: w1_q[o] fp8 [E_loc,2I,H], w1_s[o] f32 [E_loc,2I], w2_q[o] fp8 [E_loc,H,I], w2_s[o] f32 [E_loc,H].
     Returns (list of y[r] bf16 [T_r,H], RouteLayout, LayerTrace|None).
     """
-    assert variant in ("fused", "staged")
+    assert variant in ("fused", "staged", "ue8m0")
     R = len(x_q)
     E_loc = num_experts // R
     H = w2_q[0].shape[1]
@@ -339,10 +361,20 @@ def moe_layer(x_q: Sequence[torch.Tensor], x_scale: Sequence[torch.Tensor],
                 amax = act.abs().amax(dim=1)
                 s2 = (amax / FP8_MAX).clamp(min=1.0e-4)
                 aq = (act * (1.0 / s2).view(-1, 1)).to(torch.float8_e4m3fn)
+            elif variant == "ue8m0":
+                # recipe bridge to the reference's Blackwell kernel: no bf16 round trip, per-(row, 32 columns) UE8M0 scales;
+                # GEMM2 sees a * 2^e block by block (what a block-scaled MMA computes), weights keep their channel scales
+                if activation_clamp is not None:
+                    g = g.clamp(-c, c); u = u.clamp(-c, c)
+                act = g * torch.sigmoid(g) * u * wr.view(-1, 1)
+                aq, sfb = ue8m0_block_quant(act)
+                s2 = torch.ones((cnt,))
+                a2 = (aq.float().reshape(cnt, I // 32, 32) * ue8m0_to_float(sfb).unsqueeze(2)).reshape(cnt, I)
             else:
                 aq, s2, act = swiglu_quant_channelwise(torch.cat([_bf16_round(g), _bf16_round(u)], dim=1), wr, activation_clamp)
             # stage 6: GEMM2 on dequantised operands, bf16 per route
-            a2 = aq.float() * s2.view(-1, 1)
+            if variant != "ue8m0":
+                a2 = aq.float() * s2.view(-1, 1)
             w2 = w2_q[o][le].float() * w2_s[o][le].view(-1, 1)
             out = (a2 @ w2.t()).to(torch.bfloat16)
             for r in range(R):

@@ -59,6 +59,45 @@ def _worker(rank, world, port, cfg):
         dist.destroy_process_group()
 
 
+def _recipe_worker(rank, world, port, cfg):
+    """End-to-end parity of a recipe other than the default on several ranks (the stage-by-stage helpers above read the
+    channelwise recipe's intermediates)."""
+    import torch.distributed as dist
+    import megamoe
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from deepgemm_b200 import _lib
+        _lib.lib().mm_set_timeouts(20000, 4000)
+        tokens = cfg["tokens"][:world]
+        case = mc.make_case(world, cfg["E"], cfg["K"], cfg["H"], cfg["I"], tokens, seed=cfg["seed"], invalid_fraction=cfg.get("invalid", 0.0))
+        ys, lay, _ = mc.run_oracle(case, cfg.get("clamp"), cfg["oracle"])
+        e_loc = cfg["E"] // world
+        stats = torch.zeros((e_loc,), dtype=torch.int32, device="cuda")
+        y, sb = mc.run_cuda_rank(case, rank, group=dist.group.WORLD, clamp=cfg.get("clamp"), keep=True, t_max=max(max(tokens), 1),
+                                 stats=stats, recipe=getattr(megamoe, cfg["recipe"]), dispatch_num_tokens=max(tokens))
+        assert stats.cpu().tolist() == lay.totals[rank * e_loc:(rank + 1) * e_loc].tolist()
+        mc.assert_end_to_end_close(y, ys[rank], f"rank {rank}")
+        y2, _ = mc.run_cuda_rank(case, rank, group=dist.group.WORLD, clamp=cfg.get("clamp"), sb=sb, recipe=getattr(megamoe, cfg["recipe"]),
+                                 dispatch_num_tokens=max(tokens))
+        assert torch.equal(y.view(torch.int16), y2.view(torch.int16)), f"rank {rank}: not deterministic"
+        sb.destroy()
+    finally:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def test_ep2_ue8m0_recipe_uneven_tokens():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    cfg = dict(E=16, K=4, H=1024, I=512, tokens=[300, 77], seed=28, invalid=0.1, clamp=10.0, recipe="RECIPE_UE8M0_PER32", oracle="ue8m0")
+    mp.spawn(_recipe_worker, args=(2, _free_port(), cfg), nprocs=2, join=True)
+
+
 def _run(world, cfg):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")

@@ -17,7 +17,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB_NAME = "libmegamoe_b200.so"
 LIB_PATH = os.path.join(HERE, LIB_NAME)
 SOURCES = ["abi.cu", "noalloc.cu"]
-HEADERS = ["layout.h", "ptx.cuh", "route.cuh", "gemm.cuh", "gemm_pair.cuh", "misc.cuh", "deepep_layout.cuh", "split_baseline.cuh", "fused.cuh", "probe.cuh",
+HEADERS = ["layout.h", "ptx.cuh", "route.cuh", "gemm.cuh", "gemm_pair.cuh", "gemm_ue8m0.cuh", "misc.cuh", "deepep_layout.cuh", "split_baseline.cuh", "fused.cuh", "probe.cuh",
            os.path.join("..", "..", "include", "megamoe_b200.h")]
 
 

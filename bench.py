@@ -302,6 +302,49 @@ def nvlink_store_probe(dist, group, rank, world, dev, sb):
     return probe
 
 
+def tile_trace(layer, dev, cta: int, max_tiles: int = 128):
+    """One call of the layer with the layer kernel's per-tile cycle stamps switched on for one CTA (mm_set_tile_trace).
+    Per tile the kernel records the SM's clock64 when the producer took the tile / saw its dependency met / issued its last
+    copy, when the MMA issuer took it / issued its first / its last MMA, and when the first epilogue warp began to wait for the
+    accumulator / saw it complete / released it.  Returns per GEMM the medians, in SM cycles, of
+      cadence  = accumulator complete -> next accumulator complete (what a tile costs the CTA),
+      mainloop = first MMA issued -> accumulator complete,
+      epilogue = accumulator complete -> released,
+      wait     = MMA issuer took the tile -> its first operands had landed;
+    the ideal mainloop is 128 cycles per M128 x N256 x K32 MMA: 16 384 (GEMM1, K = 4096) and 8 192 (GEMM2, K = 2048)."""
+    import statistics
+    from deepgemm_b200 import _lib
+    lib = _lib.lib()
+    buf = torch.zeros((max_tiles, 12), dtype=torch.int64, device=dev)
+    _lib.check(lib.mm_set_tile_trace(buf.data_ptr(), max_tiles, cta))
+    try:
+        layer()
+        torch.cuda.synchronize()
+    finally:
+        _lib.check(lib.mm_set_tile_trace(None, 0, 0))
+    rows = [r for r in buf.cpu().tolist() if r[1] != 0]
+    out = {"cta": cta, "tiles": len(rows), "unit": "SM cycles"}
+    if not rows:
+        return out
+    t0 = rows[0][1]
+    per_kind = {0: [], 1: []}
+    prev_full = None
+    print("  j kind   tile | producer: took dep-met last-copy | mma: took first last | epilogue: wait complete released", file=sys.stderr)
+    for j, r in enumerate(rows):
+        tile, kind = r[0] & 0xffffffff, r[0] >> 32
+        pb, pd, pe, mb_, mf, me, eb, ef, ee = [(v - t0) if v else -1 for v in r[1:10]]
+        print(f"{j:3d} G{kind + 1} {tile:7d} | {pb:9d} {pd:9d} {pe:9d} | {mb_:9d} {mf:9d} {me:9d} | {eb:9d} {ef:9d} {ee:9d}", file=sys.stderr)
+        if prev_full is not None and ef > 0 and j >= 2:       # the first tiles include the start-up of the call
+            per_kind[kind].append((ef - prev_full, ef - mf, ee - ef, mf - mb_))
+        prev_full = ef
+    for kind, name in ((0, "gemm1"), (1, "gemm2")):
+        if per_kind[kind]:
+            cols = list(zip(*per_kind[kind]))
+            out[name] = {"tiles": len(per_kind[kind]), "cadence": statistics.median(cols[0]), "mainloop": statistics.median(cols[1]),
+                         "epilogue": statistics.median(cols[2]), "wait": statistics.median(cols[3])}
+    return out
+
+
 def run_sweep(args):
     """--sweep: the scaling sweep of the layer (tokens per rank x routing skew) at the launched EP size.  One JSON line per
     point from rank 0: tokens/s, FP8 TFLOP/s, NVLink GB/s per rank and the three roofline times (tensor at the measured FP8
@@ -462,6 +505,9 @@ def main():
     ap.add_argument("--profile-only", action="store_true",
                     help="device-resident arm only (no end-to-end arm, no parity or CPU baseline): the command line for ncu captures")
     ap.add_argument("--sweep", default=None, help="comma-separated tokens-per-rank list: run the scaling sweep instead of the bench")
+    ap.add_argument("--tile-trace", type=int, default=None, metavar="CTA",
+                    help="with --profile-only: after the timed steps run one more call with the layer kernel's per-tile cycle "
+                         "stamps switched on for this CTA and add their medians (SM cycles) to the line; the table goes to stderr")
     args = ap.parse_args()
     globals()["E"] = args.experts
     if args.impl == "reference":
@@ -538,9 +584,12 @@ def main():
     sb.check_status()
     if args.profile_only:
         sampler.stop()
+        line = {"profile_only": True, "ms_per_step": ms_step, "gpu_launches": launches, "experts": E, "tokens_per_rank": T,
+                "ep": world, "variant": variant}
+        if args.tile_trace is not None:
+            line["tile_trace"] = tile_trace(layer, dev, args.tile_trace)
         if rank == 0:
-            print(json.dumps({"profile_only": True, "ms_per_step": ms_step, "gpu_launches": launches, "experts": E, "tokens_per_rank": T,
-                              "ep": world, "variant": variant}), flush=True)
+            print(json.dumps(line), flush=True)
         sb.destroy()
         if dist is not None:
             dist.barrier(group)

@@ -34,6 +34,10 @@ std::atomic<int> g_pipe_ms{4000};
 // tuning switches of the layer kernel (FusedParams::policy, waves of its tile order): environment at load, or mm_set_tuning
 std::atomic<int> g_policy{[] { const char* v = getenv("MEGAMOE_HELPER_POLICY"); return v ? atoi(v) : 2; }()};
 std::atomic<int> g_wave_mblocks{[] { const char* v = getenv("MEGAMOE_WAVE_MBLOCKS"); return v ? atoi(v) : 0; }()};
+// per-tile cycle stamps of one CTA of the layer kernel (mm_set_tile_trace); null = off
+std::atomic<long long*> g_trace{nullptr};
+std::atomic<int> g_trace_cta{0};
+std::atomic<int> g_trace_tiles{0};
 
 int fail(int code, const char* fmt, ...) {
     va_list ap;
@@ -614,6 +618,9 @@ int mm_fp8_w8a8_mega_moe(void* y, const void* w1, const float* s1, const void* w
     const int wave_override = g_wave_mblocks.load();                      // tuning aid (MEGAMOE_WAVE_MBLOCKS / mm_set_tuning)
     if (wave_override != 0) fp.wave_mblocks = wave_override > 0 ? wave_override : (1 << 28);
     fp.policy = g_policy.load();                                          // tuning aid (MEGAMOE_HELPER_POLICY / mm_set_tuning)
+    fp.trace = g_trace.load();
+    fp.trace_cta = g_trace_cta.load();
+    fp.trace_tiles = g_trace_tiles.load();
     void* fused_args[] = {&tm_pool, &tm_w1, &tm_act, &tm_w2, &fp};
 
     if (mode == MM_MODE_FUSED) {
@@ -731,6 +738,14 @@ int mm_set_tuning(int policy, int wave_mblocks) {
     MM_REQUIRE(policy >= 0, "mm_set_tuning: policy must be non-negative");
     g_policy.store(policy);
     g_wave_mblocks.store(wave_mblocks);
+    return 0;
+}
+
+int mm_set_tile_trace(void* device_words, int max_tiles, int cta) {
+    MM_REQUIRE(max_tiles >= 0 && cta >= 0, "mm_set_tile_trace: bad arguments");
+    g_trace.store(max_tiles > 0 ? static_cast<long long*>(device_words) : nullptr);
+    g_trace_cta.store(cta);
+    g_trace_tiles.store(max_tiles);
     return 0;
 }
 

@@ -71,7 +71,13 @@ struct FusedParams {
     int gemm_only;         // 1: routing was done by the staged kernels; start at the tile loop and stop after it
     int policy;            // tuning switches: bit 0 = both helper warps push (default: one pushes, one requantises from the start),
                            //                  bit 1 = epilogue warps help pushing until their first accumulator is complete
+    long long* trace;      // tuning aid, normally null: per-tile cycle stamps of one CTA, kTraceWords words per tile (see TraceSlot)
+    int trace_cta, trace_tiles;
 };
+
+// Per-tile cycle stamps (clock64 of the traced CTA's SM) written by the three roles of that CTA; word 0 = tile | kind << 32.
+enum TraceSlot { TR_TILE = 0, TR_PROD_BEGIN, TR_PROD_DEP, TR_PROD_END, TR_MMA_BEGIN, TR_MMA_FIRST, TR_MMA_END, TR_EPI_BEGIN, TR_EPI_FULL,
+                 TR_EPI_END, kTraceWords = 12 };
 
 // shared-memory scratch of the routing steps, aliased onto the (not yet used) operand ring
 struct FusedRouteSmem {
@@ -341,6 +347,8 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
     // [12] helper pushes done, [13] helper requantisation done, [14] / [15] producer's own polling for GEMM1 arrivals / GEMM2 requantisation
     const uint64_t t_entry = global_timer_ns();
     auto stamp = [&](int slot) { if (blockIdx.x == 0) status[slot] = static_cast<int>((global_timer_ns() - t_entry) / 100); };
+    const bool traced = fp.trace != nullptr && static_cast<int>(blockIdx.x) == fp.trace_cta;
+    auto trace = [&](int j, int slot, long long v) { if (traced && j < fp.trace_tiles) fp.trace[j * kTraceWords + slot] = v; };
 
     // ------------------------------------------------------------------ phase 0: barriers, TMEM, call identity
     if (tid == 0) {
@@ -587,6 +595,8 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
             ring_publish(tile_ring, local_i, tile);
             int kind, mb, nb;
             order.seek(tile, kind, mb, nb);
+            trace(local_i, TR_TILE, static_cast<long long>(tile) | (static_cast<long long>(kind) << 32));
+            trace(local_i, TR_PROD_BEGIN, clock64());
             const bool second = kind == WaveOrder::kG2;
             const GemmParams& g = second ? g2 : g1;
             const int e = g.mblock_expert[mb];
@@ -627,12 +637,14 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
                     // the TMA reads
                     __threadfence_block();
                     asm volatile("fence.proxy.async;" ::: "memory");
+                    trace(local_i, TR_PROD_DEP, clock64());
                 }
                 // issue the token tile even on failure so that the stage's byte count completes and nobody is left waiting
                 tma_load_2d(a_dst, ta, kb * kBlockK, mb * kBlockM, full_bar(stage));
                 if (++stage == kStages) { stage = 0; phase ^= 1u; }
                 if (!alive) break;
             }
+            trace(local_i, TR_PROD_END, clock64());
             tile = next_tile;
         }
         ring_publish(tile_ring, local_i + 1, -1);                // no more tiles for this CTA
@@ -655,12 +667,14 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
             order.seek(tile, kind, mb, nb);
             const GemmParams& g = kind == WaveOrder::kG2 ? g2 : g1;
             const int k_blocks = g.kdim / kBlockK;
+            trace(j, TR_MMA_BEGIN, clock64());
             if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, g.timeout_ns)) { alive = false; break; }
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + acc * kBlockN;
             for (int kb = 0; kb < k_blocks; ++kb) {
                 if (!mbar_wait(full_bar(stage), phase, abort_flag, g.timeout_ns)) { alive = false; break; }
                 tc_fence_after();
+                if (kb == 0) trace(j, TR_MMA_FIRST, clock64());
                 const uint32_t a_src = smem_base + stage * kStageBytes;
                 const uint64_t da = umma_desc_k_sw128(a_src);
                 const uint64_t db = umma_desc_k_sw128(a_src + kABytes);
@@ -670,6 +684,7 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
                 if (kb == k_blocks - 1) umma_commit(tfull_bar(acc));
                 if (++stage == kStages) { stage = 0; phase ^= 1u; }
             }
+            trace(j, TR_MMA_END, clock64());
             if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
         }
         stamp(8);
@@ -819,8 +834,10 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
                 raw = __ldcg(reinterpret_cast<const uint4*>(g.meta + row));
                 if (second) a_scale = __ldcg(g.act_scale + row);
             }
+            if (is_scout) trace(local_i, TR_EPI_BEGIN, clock64());
             if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, g.timeout_ns)) { alive = false; break; }
             tc_fence_after();
+            if (is_scout) trace(local_i, TR_EPI_FULL, clock64());
             // the accumulator is complete, so the m-block's rows (and, for GEMM2, its activation scales) are in place
             float row_scale = 0.0f, route_w = 0.0f;
             uint8_t* out_ptr = nullptr;
@@ -842,6 +859,7 @@ mega_moe_fused_kernel(const __grid_constant__ CUtensorMap tm_pool, const __grid_
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty_bar(acc));
+            if (is_scout) trace(local_i, TR_EPI_END, clock64());
             if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
 
             // this warp's share of a GEMM1 tile (bf16 values, row amax) is stored: it is counted towards the m-block's total at

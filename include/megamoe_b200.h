@@ -122,6 +122,13 @@ int mm_set_timeouts(int rank_barrier_ms, int pipeline_ms);
  * MEGAMOE_WAVE_MBLOCKS at load time.  All ranks of a group must use the same values. */
 int mm_set_tuning(int policy, int wave_mblocks);
 
+/* Tuning aid: per-tile cycle stamps of one CTA of the layer kernel.  device_words: max_tiles x 12 int64 words in device
+ * memory (zeroed by the caller), filled by later calls: word 0 = tile index | kind << 32 (0 = GEMM1, 1 = GEMM2), then the
+ * SM's clock64 when the producer took the tile / saw its dependency met / issued its last copy, when the MMA issuer took
+ * it / issued its first / its last MMA, when the first epilogue warp began waiting for the accumulator / saw it complete /
+ * released it.  max_tiles = 0 switches the trace off.  Not for production: the stamps cost a few stores per tile. */
+int mm_set_tile_trace(void* device_words, int max_tiles, int cta);
+
 /* JSON description of the build.  Replaces get_mega_moe_hip_build_config, csrc/apis/mega_dcu.hpp:28-39. */
 int mm_build_config(char* json, int capacity);
 

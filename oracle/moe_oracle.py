@@ -26,7 +26,8 @@ own quantisation helpers are torch code, so torch's fp8 cast is the authoritativ
 
 Parity pin: stages 1-2 (and the Marlin permutation) are checked bit-for-bit against outputs of the
 reference's own torch helpers imported from the reference tree (tests/golden/make_golden.py ->
-tests/golden/ref_quant.npz).  Stages 3-7 have no golden vector, known-answer test or runnable
+tests/golden/ref_quant.npz), and so is the per-32 UE8M0 quantiser of variant "ue8m0" (ue8m0_block_quant
+against deep_gemm/utils/math.py:13-37, tests/golden/ref_ue8m0.npz).  Stages 3-7 have no golden vector, known-answer test or runnable
 implementation anywhere in the reference: PARITY UNPINNED for those stages; the acceptance bar is
 the one the task states (routing layout bit-exact against this restatement, outputs within
 max-abs <= 2e-2 * rms and cosine >= 0.999).

@@ -4,13 +4,18 @@ Run where a checkout of the reference project is available, giving its root dire
 
     python tests/golden/make_golden.py <reference root>          # or MEGAMOE_REFERENCE_ROOT=<reference root>
 
-Two kinds of fixture are written:
+    python tests/golden/make_golden.py <reference root> --only ue8m0     # just ref_ue8m0.npz
+
+Three kinds of fixture are written:
 
 * ``ref_quant.npz`` -- outputs of the REFERENCE'S OWN torch helpers (``megamoe/__init__.py``:
   ``cast_to_fp8_channelwise``, ``cast_grouped_weight_to_fp8_channelwise``, ``weight8bit_nt_kpack2_marlin``,
   ``transform_fp8_weights_for_mega_moe``, ``_large_opt_3stage_selected``) on seeded inputs.  The reference package
   imports a HIP extension ``megamoe._C`` at import time; a stub module with that name is installed first so the
   pure-torch helpers can be imported unmodified.  These vectors pin the oracle's quantisation stages.
+* ``ref_ue8m0.npz`` -- outputs of the reference's torch helper ``per_token_cast_to_fp8(x, use_ue8m0=True, gran_k=32)``
+  (``deep_gemm/utils/math.py:13-37``, loaded from its file: the package itself imports a CUDA extension) on seeded
+  inputs: e4m3 codes and power-of-two scales per (row, 32 columns).  Pins ``oracle.moe_oracle.ue8m0_block_quant``.
 * ``layer_small.npz`` -- inputs and outputs of the CPU oracle (oracle/moe_oracle.py) for the small configuration
   (256 tokens, hidden 512, intermediate 256, 8 experts, top-2, seed 0) and a 2-rank variant.  The reference has no
   runnable implementation of the layer, so these are regression vectors of the restatement, not reference outputs.
@@ -63,10 +68,37 @@ def edge_values():
     return torch.cat([allv, -allv]).contiguous()
 
 
+def write_ue8m0(ref_root: str):
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("_ref_dg_math", os.path.join(ref_root, "deep_gemm", "utils", "math.py"))
+    m = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(m)
+    g = torch.Generator().manual_seed(7)
+    x = torch.randn((48, 256), generator=g)
+    x *= torch.exp2(torch.randint(-8, 9, (48, 1), generator=g).float())          # rows over 16 octaves
+    # blocks whose amax sits on, just below and just above a scale boundary (448 * 2^e), and a block of small values
+    for i, (e, f) in enumerate([(0, 1.0), (0, 1.0 - 2.0 ** -24), (0, 1.0 + 2.0 ** -23), (-3, 1.0), (5, 1.0 + 2.0 ** -23), (2, 0.75)]):
+        x[i, :32] = torch.linspace(-0.9, 0.9, 32) * 448.0 * 2.0 ** e
+        x[i, 7] = 448.0 * 2.0 ** e * f
+    x[6, 32:64] = torch.linspace(-1, 1, 32) * 3e-4                                # above the helper's 1e-4 floor on amax
+    q, sf = m.per_token_cast_to_fp8(x, use_ue8m0=True, gran_k=32)
+    out = {"x": x.numpy(), "q": q.view(torch.uint8).numpy(), "sf": sf.numpy()}
+    np.savez_compressed(os.path.join(HERE, "ref_ue8m0.npz"), **out)
+    print("wrote ref_ue8m0.npz", {k: v.shape for k, v in out.items()})
+
+
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("MEGAMOE_REFERENCE_ROOT")
+    args = [a for a in sys.argv[1:] if not a.startswith("--")]
+    ref_root = args[0] if args else os.environ.get("MEGAMOE_REFERENCE_ROOT")
     if not ref_root or not os.path.isdir(ref_root):
-        raise SystemExit("usage: make_golden.py <root of the reference checkout>")
+        raise SystemExit("usage: make_golden.py <root of the reference checkout> [--only ue8m0]")
+    if "--only" in sys.argv:
+        what = sys.argv[sys.argv.index("--only") + 1]
+        if what != "ue8m0":
+            raise SystemExit("--only knows: ue8m0")
+        write_ue8m0(ref_root)
+        return
+    write_ue8m0(ref_root)
     ref = import_reference_megamoe(ref_root)
     out = {}
     g = torch.Generator().manual_seed(0)

@@ -146,3 +146,22 @@ def test_quantised_layer_tracks_unquantised_bf16_model():
             ref[t] += case.w2_bf16[0][e].float() @ a
     err, cos = orc.parity_metrics(y[0], ref)
     assert cos > 0.995 and err < 0.5, (err, cos)
+
+
+def test_ue8m0_block_quantiser_matches_the_reference_helper():
+    """oracle.ue8m0_block_quant against per_token_cast_to_fp8(x, use_ue8m0=True, gran_k=32) of the reference
+    (deep_gemm/utils/math.py:13-37; fixture ref_ue8m0.npz): codes and power-of-two scales bit for bit, including blocks
+    whose amax sits on, one ulp below and one ulp above a scale boundary (448 * 2^e).  The helper floors amax at 1e-4;
+    the fixture stays above that floor, where the reference's kernel (no floor) and its helper agree."""
+    d = np.load(os.path.join(GOLD, "ref_ue8m0.npz"))
+    x = torch.from_numpy(d["x"].copy())
+    q, byte = orc.ue8m0_block_quant(x)
+    assert np.array_equal(orc.ue8m0_to_float(byte).numpy(), d["sf"])
+    assert np.array_equal(q.view(torch.uint8).numpy(), d["q"])
+    # boundary blocks: amax == 448 * 2^e keeps e, one ulp more takes e + 1
+    assert byte[0, 0].item() == 127 and byte[1, 0].item() == 127 and byte[2, 0].item() == 128
+    assert byte[3, 0].item() == 124 and byte[4, 0].item() == 133
+    # every scale is the smallest power of two that keeps the block inside +-448
+    amax = x.reshape(48, 8, 32).abs().amax(dim=2)
+    sf = orc.ue8m0_to_float(byte)
+    assert bool((amax <= 448.0 * sf).all()) and bool((amax > 448.0 * sf / 2).all())

@@ -509,6 +509,8 @@ def main():
                     help="with --profile-only: after the timed steps run one more call with the layer kernel's per-tile cycle "
                          "stamps switched on for this CTA and add their medians (SM cycles) to the line; the table goes to stderr")
     args = ap.parse_args()
+    if args.tile_trace is not None and not args.profile_only:
+        ap.error("--tile-trace needs --profile-only")
     globals()["E"] = args.experts
     if args.impl == "reference":
         run_reference_arm(args)

@@ -715,14 +715,17 @@ def main():
         fp8_rand = _lib.fp8_mma_peak_tflops(random_operands=True)
         if kernel_flops / (fp8_rand * 1e12) > kernel_bytes / (hbm_peak * 1e9):
             fp8_ones = _lib.fp8_mma_peak_tflops(random_operands=False)
+            fp8_quant = _lib.fp8_mma_peak_tflops(quantised_like_operands=True)
             bf16 = measured_bf16_tflops()
             tf = kernel_flops / (kernel_ms * 1e-3) / 1e12
             roofline = {"kernel": kernel_name, "bound": "tensor", "achieved": tf, "peak": fp8_rand, "unit": "TFLOP/s",
                         "frac": tf / fp8_rand, "peak_kind": "of measured: own FP8 MMA probe with random operands, burst "
                         "(MEASURED_PEAKS.json holds a bf16 figure only)",
                         "fp8_peak_candidates_tflops": {"probe_random_operands": round(fp8_rand, 1), "probe_ones_operands": round(fp8_ones, 1),
+                                                       "probe_quantised_like_operands": round(fp8_quant, 1),
                                                        "twice_measured_bf16": None if bf16 is None else round(2 * bf16, 1)},
                         "frac_of": {"probe_ones_operands": round(tf / fp8_ones, 4),
+                                    "probe_quantised_like_operands": round(tf / fp8_quant, 4),
                                     "twice_measured_bf16": None if bf16 is None else round(tf / (2 * bf16), 4)},
                         "traffic": None, "traffic_note": "tensor-bound: see profiles/ for the pipe-utilisation capture",
                         "algorithmic_flops": kernel_flops, "algorithmic_bytes": kernel_bytes, "ms": kernel_ms}

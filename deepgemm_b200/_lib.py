@@ -119,9 +119,12 @@ def stage_times() -> dict:
     return {n: float(v) for n, v in zip(STAGE_NAMES, buf) if v >= 0}
 
 
-def fp8_mma_peak_tflops(iters: int = 20000, repeats: int = 5, random_operands: bool = False, cta_pair: bool = False) -> float:
+def fp8_mma_peak_tflops(iters: int = 20000, repeats: int = 5, random_operands: bool = False, cta_pair: bool = False,
+                        quantised_like_operands: bool = False) -> float:
     """Dense FP8 tensor-core rate (TFLOP/s) measured with the library's probe kernel on the current device (best of repeats).
-    random_operands: pseudo-random e4m3 data instead of all ones (draws more power, so the clock and the rate are lower)."""
+    random_operands: pseudo-random e4m3 data of magnitude below 2 instead of all ones; quantised_like_operands: e4m3 codes
+    with the exponent fields per-row quantisation of N(0,1) data produces.  Both draw more power than all ones, so under
+    the board's power cap the clock and the rate are lower (the cycle count per MMA is the same)."""
     import torch
     status = torch.zeros((1,), dtype=torch.int32, device="cuda")
     stream = torch.cuda.current_stream().cuda_stream
@@ -130,7 +133,8 @@ def fp8_mma_peak_tflops(iters: int = 20000, repeats: int = 5, random_operands: b
     for _ in range(repeats + 1):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        check(lib().mm_fp8_mma_peak_probe(iters, int(random_operands), int(cta_pair), status.data_ptr(), stream, ctypes.byref(flops)))
+        check(lib().mm_fp8_mma_peak_probe(iters, 2 if quantised_like_operands else int(random_operands), int(cta_pair), status.data_ptr(), stream,
+                                          ctypes.byref(flops)))
         e1.record()
         torch.cuda.synchronize()
         best = max(best, flops.value / (e0.elapsed_time(e1) * 1e-3) / 1e12)

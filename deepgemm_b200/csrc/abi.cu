@@ -478,7 +478,7 @@ int mm_swiglu_quant_channelwise(const void* x_bf16, const float* weights, const 
 }
 
 int mm_fp8_mma_peak_probe(int iters, int operands, int cta_pair, int* status_dev, void* stream_, double* flops_out) {
-    MM_REQUIRE(iters > 0 && status_dev && (operands == 0 || operands == 1) && (cta_pair == 0 || cta_pair == 1),
+    MM_REQUIRE(iters > 0 && status_dev && operands >= 0 && operands <= 2 && (cta_pair == 0 || cta_pair == 1),
                "mm_fp8_mma_peak_probe: bad arguments");
     int sms = 0;
     if (int rc = sm_count(&sms)) return rc;

@@ -201,8 +201,10 @@ int mm_swiglu_quant_channelwise(const void* x_bf16, const float* weights, const 
  * launch a kernel that issues `iters` groups of eight dense FP8 MMAs (tcgen05 kind::f8f6f4, M128 x N256 x K32 per SM) from
  * operands resident in shared memory.  *flops_out receives the floating-point operations of the launch; time it with events
  * on `stream` to get the tensor-core rate the GEMM kernels can at best reach.
- *   operands: 0 = every byte 1.0 (few bits toggle: the burst rate), 1 = pseudo-random finite e4m3 values of both signs
- *             (the power draw of real data; under the board's power cap the sustained rate is lower and falls over seconds);
+ *   operands: 0 = every byte 1.0 (few bits toggle: the burst rate), 1 = pseudo-random finite e4m3 values of both signs and
+ *             magnitude below 2, 2 = e4m3 codes as per-row quantisation of N(0,1) data produces them (exponent fields 9..14,
+ *             random sign and mantissa).  The cycle count per MMA is the same for all three (128); the power draw is not,
+ *             and under the board's power cap the clock -- and with it the rate -- falls from 0 to 1 to 2;
  *   cta_pair: 0 = cta_group::1 MMAs, 1 = cta_group::2 MMAs (M256 over two SMs) as the CTA-pair GEMM kernels issue them.
  * status_dev: a zeroed device int. */
 int mm_fp8_mma_peak_probe(int iters, int operands, int cta_pair, int* status_dev, void* stream, double* flops_out);

@@ -416,3 +416,17 @@ def test_graph_bucket_mode_uses_device_side_token_count(variant):
             mc.assert_layer_close(y[:n].cpu(), ys[0][:n], f"graph replay with {n} tokens")
         assert bool((y[n:] == 7.0).all()), "rows past the device-side token count must not be written"
     sb.destroy()
+
+
+def test_fp8_probe_runs_with_every_operand_class():
+    """The FP8 MMA probe (the denominator of tensor-bound roofline fractions) with all-ones, pseudo-random and
+    quantised-like operands, one-CTA and CTA-pair form: finishes with a clean status and a plausible rate."""
+    from deepgemm_b200 import _lib
+    rates = {
+        "ones": _lib.fp8_mma_peak_tflops(iters=2000, repeats=1),
+        "random": _lib.fp8_mma_peak_tflops(iters=2000, repeats=1, random_operands=True),
+        "quantised": _lib.fp8_mma_peak_tflops(iters=2000, repeats=1, quantised_like_operands=True),
+        "pair": _lib.fp8_mma_peak_tflops(iters=2000, repeats=1, cta_pair=True),
+    }
+    for name, tf in rates.items():
+        assert 500.0 < tf < 6000.0, (name, rates)        # nominal dense FP8: 4500 TFLOP/s

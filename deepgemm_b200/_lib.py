@@ -50,6 +50,7 @@ _SIGNATURES = {
     "mm_set_timeouts": (c_int, [c_int, c_int]),
     "mm_set_tuning": (c_int, [c_int, c_int]),
     "mm_set_tile_trace": (c_int, [c_void_p, c_int, c_int]),
+    "mm_tile_order": (c_int, [c_int, c_int, c_int, c_int, c_int, POINTER(c_int32)]),
     "mm_build_config": (c_int, [ctypes.c_char_p, c_int]),
     "mm_launch_count": (c_int64, []),
     "mm_fp8_w8a8_mega_moe_static": (c_int, [c_void_p] * 10 + [c_int] * 5 + [c_float, c_void_p]),

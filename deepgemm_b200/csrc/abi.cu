@@ -741,6 +741,18 @@ int mm_set_tuning(int policy, int wave_mblocks) {
     return 0;
 }
 
+int mm_tile_order(int num_mblocks, int wave_mblocks, int gemm1_blocks, int gemm2_blocks, int tile_interleave, int32_t* out3) {
+    MM_REQUIRE(num_mblocks >= 0 && wave_mblocks > 0 && gemm1_blocks > 0 && gemm2_blocks > 0 && out3, "mm_tile_order: bad arguments");
+    mm::WaveOrder order(num_mblocks, wave_mblocks, gemm1_blocks, gemm2_blocks, tile_interleave != 0);
+    const int64_t tiles = (int64_t)num_mblocks * (gemm1_blocks + gemm2_blocks);
+    for (int64_t t = 0; t < tiles; ++t) {
+        int kind, mb, nb;
+        order.seek((int)t, kind, mb, nb);
+        out3[3 * t] = kind; out3[3 * t + 1] = mb; out3[3 * t + 2] = nb;
+    }
+    return 0;
+}
+
 int mm_set_tile_trace(void* device_words, int max_tiles, int cta) {
     MM_REQUIRE(max_tiles >= 0 && cta >= 0, "mm_set_tile_trace: bad arguments");
     g_trace.store(max_tiles > 0 ? static_cast<long long*>(device_words) : nullptr);

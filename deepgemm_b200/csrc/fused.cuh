@@ -132,11 +132,15 @@ struct WaveOrder {
     int n_waves, wave_m, num_mblocks, nb1, nb2;
     int g, base, size, n1, n2, w1, w2;          // current group: n1 GEMM1 tiles of wave w1, n2 GEMM2 tiles of wave w2
     bool tile_interleave;                       // false: inside a group all GEMM1 tiles come before the GEMM2 tiles
-    __device__ WaveOrder(int num_mblocks_, int wave_m_, int nb1_, int nb2_, bool tile_interleave_)
+    __host__ __device__ WaveOrder(int num_mblocks_, int wave_m_, int nb1_, int nb2_, bool tile_interleave_)
         : n_waves((num_mblocks_ + wave_m_ - 1) / wave_m_), wave_m(wave_m_), num_mblocks(num_mblocks_), nb1(nb1_), nb2(nb2_),
           g(0), base(0), tile_interleave(tile_interleave_) { set(); }
-    __device__ __forceinline__ int wave_mblocks(int w) const { return w < n_waves ? min(wave_m, num_mblocks - w * wave_m) : 0; }
-    __device__ __forceinline__ void set() {
+    __host__ __device__ __forceinline__ int wave_mblocks(int w) const {
+        if (w >= n_waves) return 0;
+        const int left = num_mblocks - w * wave_m;
+        return left < wave_m ? left : wave_m;
+    }
+    __host__ __device__ __forceinline__ void set() {
         w1 = g;
         w2 = g - kWaveLookahead;
         n1 = wave_mblocks(w1) * nb1;
@@ -144,10 +148,10 @@ struct WaveOrder {
         size = n1 + n2;
     }
     // tile -> (kind, m-block, n-block); the caller guarantees tile < num_mblocks * (nb1 + nb2)
-    __device__ __forceinline__ void seek(int tile, int& kind_out, int& mb, int& nb) {
+    __host__ __device__ __forceinline__ void seek(int tile, int& kind_out, int& mb, int& nb) {
         while (tile >= base + size) { base += size; ++g; set(); }
         const int r = tile - base;
-        const int m = tile_interleave ? min(n1, n2) : 0;
+        const int m = tile_interleave ? (n1 < n2 ? n1 : n2) : 0;
         int idx;
         if (r < 2 * m) { kind_out = (r & 1) ? kG2 : kG1; idx = r >> 1; }
         else if (tile_interleave) { kind_out = n1 > n2 ? kG1 : kG2; idx = r - m; }

@@ -122,6 +122,14 @@ int mm_set_timeouts(int rank_barrier_ms, int pipeline_ms);
  * MEGAMOE_WAVE_MBLOCKS at load time.  All ranks of a group must use the same values. */
 int mm_set_tuning(int policy, int wave_mblocks);
 
+/* Test hook (host only, no device work): the layer kernel's tile order.  out3 receives, for tile index t = 0 ..
+ * num_mblocks * (gemm1_blocks + gemm2_blocks) - 1, the triple {kind (0 = GEMM1, 1 = GEMM2), m-block, n-block} that the kernel's
+ * own order object yields -- the same code the device runs.  The order replaces the reference's wave scheduler
+ * (deep_gemm/include/deep_gemm/scheduler/mega_moe.cuh:116-181); the kernel's freedom from deadlock rests on two of its
+ * properties, which the CPU tests check: every tile appears exactly once, and every GEMM2 tile of an m-block comes after all
+ * GEMM1 tiles of that m-block. */
+int mm_tile_order(int num_mblocks, int wave_mblocks, int gemm1_blocks, int gemm2_blocks, int tile_interleave, int32_t* out3);
+
 /* Tuning aid: per-tile cycle stamps of one CTA of the layer kernel.  device_words: max_tiles x 12 int64 words in device
  * memory (zeroed by the caller), filled by later calls: word 0 = tile index | kind << 32 (0 = GEMM1, 1 = GEMM2), then the
  * SM's clock64 when the producer took the tile / saw its dependency met / issued its last copy, when the MMA issuer took

@@ -152,3 +152,63 @@ def test_cpu_tensors_are_refused():
         megamoe.cast_to_fp8_channelwise(torch.zeros((2, 16), dtype=torch.bfloat16))
     with pytest.raises(ValueError):
         megamoe.cast_to_fp8_channelwise(torch.zeros((16,), dtype=torch.bfloat16))
+
+
+def _tile_order(lib, num_mblocks, wave_m, nb1, nb2, interleave):
+    import numpy as np
+    n = num_mblocks * (nb1 + nb2)
+    out = np.zeros((max(n, 1), 3), dtype=np.int32)
+    rc = lib.mm_tile_order(num_mblocks, wave_m, nb1, nb2, int(interleave), out.ctypes.data_as(ctypes.POINTER(ctypes.c_int32)))
+    assert rc == 0, lib.mm_last_error()
+    return out[:n]
+
+
+@pytest.mark.parametrize("interleave", [True, False])
+def test_tile_order_is_a_permutation_with_backward_dependencies(built_lib, interleave):
+    """The layer kernel's tile order, produced by the same code the device runs (mm_tile_order): every GEMM1 and GEMM2
+    tile exactly once; every GEMM2 tile of an m-block after ALL GEMM1 tiles of that m-block (the kernel's waits then only
+    ever point at earlier tiles, which is what rules out a cycle); GEMM1 m-blocks start in ascending order (the order the
+    requantisation units are claimed in)."""
+    import numpy as np
+    rng = np.random.default_rng(0)
+    shapes = [(0, 3, 16, 16), (1, 1, 1, 1), (1, 19, 16, 16), (2, 1, 3, 2), (32, 19, 16, 16), (192, 19, 16, 16), (257, 7, 2, 5),
+              (40, 1 << 28, 16, 16), (5, 2, 1, 9), (64, 3, 9, 1)]
+    shapes += [tuple(int(v) for v in (rng.integers(1, 300), rng.integers(1, 40), rng.integers(1, 20), rng.integers(1, 20))) for _ in range(40)]
+    for num_mblocks, wave_m, nb1, nb2 in shapes:
+        order = _tile_order(built_lib, num_mblocks, wave_m, nb1, nb2, interleave)
+        assert order.shape[0] == num_mblocks * (nb1 + nb2)
+        if num_mblocks == 0:
+            continue
+        kind, mb, nb = order[:, 0], order[:, 1], order[:, 2]
+        assert set(np.unique(kind)) <= {0, 1}
+        g1 = np.nonzero(kind == 0)[0]; g2 = np.nonzero(kind == 1)[0]
+        key1 = mb[g1].astype(np.int64) * nb1 + nb[g1]
+        key2 = mb[g2].astype(np.int64) * nb2 + nb[g2]
+        assert np.array_equal(np.sort(key1), np.arange(num_mblocks * nb1)), (num_mblocks, wave_m, nb1, nb2)
+        assert np.array_equal(np.sort(key2), np.arange(num_mblocks * nb2)), (num_mblocks, wave_m, nb1, nb2)
+        assert (nb[g1] < nb1).all() and (nb[g2] < nb2).all() and (mb >= 0).all() and (mb < num_mblocks).all()
+        last_g1 = np.full(num_mblocks, -1); first_g2 = np.full(num_mblocks, order.shape[0])
+        np.maximum.at(last_g1, mb[g1], g1)
+        np.minimum.at(first_g2, mb[g2], g2)
+        assert (last_g1 < first_g2).all(), (num_mblocks, wave_m, nb1, nb2)
+        first_g1 = np.full(num_mblocks, order.shape[0]); np.minimum.at(first_g1, mb[g1], g1)
+        assert (np.diff(first_g1) > 0).all()
+
+
+def test_tile_order_keeps_gemm2_three_waves_behind_gemm1(built_lib):
+    """Default shape of the order (two rounds of GEMM1 tiles per wave, GEMM2 of wave k beside GEMM1 of wave k + 3): a
+    GEMM2 tile of m-block b never comes before the first GEMM1 tile of m-block b + 3 * wave (its requantisation has three
+    waves of GEMM1 work to finish behind), and inside a mixed group the two kinds alternate tile by tile."""
+    import numpy as np
+    num_mblocks, wave_m, nb1, nb2 = 192, 19, 16, 16
+    order = _tile_order(built_lib, num_mblocks, wave_m, nb1, nb2, True)
+    kind, mb = order[:, 0], order[:, 1]
+    first_g1 = np.full(num_mblocks, order.shape[0]); np.minimum.at(first_g1, mb[kind == 0], np.nonzero(kind == 0)[0])
+    for t in np.nonzero(kind == 1)[0]:
+        ahead = mb[t] // wave_m * wave_m + 3 * wave_m
+        if ahead < num_mblocks:
+            assert first_g1[ahead] < t
+    # the first three waves are GEMM1 only; then the kinds alternate
+    assert (kind[:3 * wave_m * nb1] == 0).all()
+    mixed = kind[3 * wave_m * nb1: 3 * wave_m * nb1 + 2 * wave_m * nb1]
+    assert (mixed[0::2] == 0).all() and (mixed[1::2] == 1).all()

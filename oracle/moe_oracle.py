@@ -73,6 +73,7 @@ def clib():
         lib.orc_e4m3_encode_array.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64]
         lib.orc_e4m3_decode_array.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64]
         lib.orc_quant_rows.argtypes = [ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p]
+        lib.orc_ue8m0_quant_rows.argtypes = [ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p]
         lib.orc_route_layout.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                                          ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                          ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
@@ -101,6 +102,17 @@ def c_quant_rows(x: np.ndarray):
     q = np.empty((rows, k), dtype=np.uint8)
     s = np.empty((rows,), dtype=np.float32)
     clib().orc_quant_rows(x.ctypes.data, rows, k, q.ctypes.data, s.ctypes.data)
+    return q, s
+
+
+def c_ue8m0_quant_rows(x: np.ndarray):
+    """C restatement of ue8m0_block_quant: (codes uint8 [rows, k], scale bytes uint8 [rows, k / 32])."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    rows, k = x.shape
+    assert k % 32 == 0
+    q = np.empty((rows, k), dtype=np.uint8)
+    s = np.empty((rows, k // 32), dtype=np.uint8)
+    clib().orc_ue8m0_quant_rows(x.ctypes.data, rows, k, q.ctypes.data, s.ctypes.data)
     return q, s
 
 

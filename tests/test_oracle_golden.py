@@ -165,3 +165,16 @@ def test_ue8m0_block_quantiser_matches_the_reference_helper():
     amax = x.reshape(48, 8, 32).abs().amax(dim=2)
     sf = orc.ue8m0_to_float(byte)
     assert bool((amax <= 448.0 * sf).all()) and bool((amax > 448.0 * sf / 2).all())
+
+
+def test_c_ue8m0_quantiser_matches_the_reference_helper_and_the_torch_restatement():
+    d = np.load(os.path.join(GOLD, "ref_ue8m0.npz"))
+    q, byte = orc.c_ue8m0_quant_rows(d["x"])
+    assert np.array_equal(q, d["q"])
+    assert np.array_equal((byte.astype(np.int32) << 23).view(np.float32), d["sf"])
+    # tiny and zero blocks (below the torch helper's 1e-4 floor, where the kernel's rule applies): C == torch restatement
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn((8, 128), generator=g) * torch.tensor([1e-30, 1e-12, 1e-6, 1e-5, 0.0, 1.0, 1e4, 3e38]).view(8, 1)
+    tq, tb = orc.ue8m0_block_quant(x)
+    cq, cb = orc.c_ue8m0_quant_rows(x.numpy())
+    assert np.array_equal(cb, tb.numpy()) and np.array_equal(cq, tq.view(torch.uint8).numpy())
